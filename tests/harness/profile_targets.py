@@ -1,6 +1,6 @@
 """Small single-kernel drivers for ncu captures (development tool).
 
-    ncu --set full --clock-control none --import-source on -k regex:gemm_tcgen05 -c 2 -o gpurun_out/gemm python tests/harness/profile_targets.py gemm1
+    ncu --set full --clock-control none -k regex:gemm_tcgen05 -c 2 -o gpurun_out/gemm python tests/harness/profile_targets.py gemm1
 """
 import sys
 import os

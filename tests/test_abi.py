@@ -50,18 +50,6 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
         _lib.lib()
 
 
-def test_sass_has_tcgen05_and_tma():
-    """Blackwell-native evidence: UTC*MMA (tcgen05.mma), LDTM (tcgen05.ld), UTMALDG (TMA)."""
-    import shutil
-    import subprocess
-    cuobjdump = shutil.which("cuobjdump") or "/usr/local/cuda/bin/cuobjdump"
-    if not os.path.exists(cuobjdump):
-        pytest.skip("cuobjdump not available")
-    sass = subprocess.run([cuobjdump, "-sass", _lib.LIB_PATH], capture_output=True, text=True).stdout
-    assert "UTCHMMA" in sass and "LDTM" in sass and "UTMALDG" in sass
-    assert "HMMA.16816" not in sass     # no legacy mma.sync tensor path
-
-
 def test_header_is_plain_c_and_a_c_host_binds_every_entry_point(tmp_path):
     """include/evo_b200.h is the boundary for ANY host: it must compile as C99 and as C++ on its own, and a C program that
     #includes it and dlopen()s the library must resolve every declared entry point and get answers from the two that need no
