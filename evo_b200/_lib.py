@@ -66,6 +66,38 @@ class LoopParams(C.Structure):
                 ("seed", C.c_uint64), ("step0", C.c_int64)]
 
 
+class ResidNormParams(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("y", C.c_void_p), ("ldy", C.c_int64), ("y_dtype", C.c_int), ("y_scale", C.c_float),
+                ("x_add", C.c_void_p), ("weight", C.c_void_p), ("weight_offset", C.c_float), ("eps", C.c_float),
+                ("out", C.c_void_p), ("ldo", C.c_int64), ("out_dtype", C.c_int),
+                ("B", C.c_int), ("seq_len", C.c_int64), ("halo", C.c_int64), ("D", C.c_int),
+                ("halo_src", C.c_void_p), ("gather", C.c_void_p)]
+
+
+class CausalConvParams(C.Structure):
+    _fields_ = [("inp", C.c_void_p), ("weight", C.c_void_p), ("out", C.c_void_p), ("ldo", C.c_int64), ("out_dtype", C.c_int),
+                ("carry_out", C.c_void_p), ("B", C.c_int), ("seq_len", C.c_int64), ("D", C.c_int), ("taps", C.c_int)]
+
+
+class Hgrn2Params(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("f", C.c_void_p), ("v", C.c_void_p), ("ld", C.c_int64),
+                ("f_bias", C.c_void_p), ("lower", C.c_void_p), ("norm_w", C.c_void_p), ("eps", C.c_float),
+                ("state", C.c_void_p), ("zero_start", C.c_int),
+                ("out", C.c_void_p), ("ldo", C.c_int64), ("dtype", C.c_int),
+                ("B", C.c_int), ("L", C.c_int64), ("H", C.c_int), ("dk", C.c_int), ("dv", C.c_int)]
+
+
+class WindowAttnParams(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("q_tok_stride", C.c_int64),
+                ("k", C.c_void_p), ("v", C.c_void_p), ("k_tok_stride", C.c_int64), ("v_tok_stride", C.c_int64),
+                ("k_batch_stride", C.c_int64), ("v_batch_stride", C.c_int64),
+                ("gate", C.c_void_p), ("gate_tok_stride", C.c_int64),
+                ("out", C.c_void_p), ("ldo", C.c_int64), ("dtype", C.c_int),
+                ("B", C.c_int), ("Lq", C.c_int64), ("H", C.c_int), ("G", C.c_int), ("dk", C.c_int), ("dv", C.c_int), ("n_maps", C.c_int),
+                ("q_pos0", C.c_int64), ("pos_dev", C.c_void_p), ("window", C.c_int64), ("keep_first", C.c_int64),
+                ("scale", C.c_float), ("lambda_", C.c_float), ("head_norm", C.c_int), ("norm_eps", C.c_float), ("out_scale", C.c_float)]
+
+
 # name -> (restype, argtypes); every symbol include/evo_b200.h declares
 SIGNATURES = {
     "evo_last_error": (C.c_char_p, []),
@@ -102,6 +134,15 @@ SIGNATURES = {
     "evo_unembed_score": (C.c_int, [C.POINTER(ScoreParams), C.c_void_p]),
     "evo_tokenize_pad": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "evo_logprobs": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]),
+    "evo_embed_f32": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
+    "evo_resid_norm": (C.c_int, [C.POINTER(ResidNormParams), C.c_void_p]),
+    "evo_causal_conv": (C.c_int, [C.POINTER(CausalConvParams), C.c_void_p]),
+    "evo_polynorm": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_float, C.c_int, C.c_void_p]),
+    "evo_softcap_logits": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_int, C.c_void_p]),
+    "evo_copy_rows": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_int64, C.c_int, C.c_int64, C.c_void_p, C.c_int, C.c_void_p]),
+    "evo_hgrn2_fwd": (C.c_int, [C.POINTER(Hgrn2Params), C.c_void_p]),
+    "evo_window_attn_fwd": (C.c_int, [C.POINTER(WindowAttnParams), C.c_void_p]),
+    "evo_gemm_simt": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
 }
 
 _lib = None

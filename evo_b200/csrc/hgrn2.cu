@@ -1,0 +1,146 @@
+// Gated linear recurrence (HGRN2) as one fused kernel: gate activation (sigmoid with a learned lower bound), query
+// activation (SiLU), the matrix-state recurrence S <- diag(g) S + (1 - g) v^T, the read-out o = S^T q and the per-head
+// RMS norm with weight.  Everything after the raw projections is fp32, and the state stays in registers for the whole
+// sequence: HBM sees q, f, v once, the output once and the state once per call.
+//
+// One CTA per (head, sequence).  A thread owns RPT consecutive state rows of one value channel: thread (kp, j) holds
+// S[kp*RPT .. kp*RPT+RPT) [j]; 16 tokens of activated gates / queries / values are staged in shared memory per round, so the
+// time loop runs without barriers; partial read-outs of the dk/RPT row groups are folded after each round.
+// The same kernel serves the single-token step (L == 1): the state is then streamed through once.
+#include "common.cuh"
+#include "../../include/evo_b200.h"
+
+using namespace evo;
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+constexpr int TCH = 16;      // tokens staged per round
+
+template <typename T, int RPT>
+__global__ void __launch_bounds__(RPT <= 16 ? 1024 : (RPT == 32 ? 512 : 256)) hgrn2_kernel(evo_hgrn2_params p, int KP, int dvp) {
+  extern __shared__ float smem[];
+  const int dk = p.dk, dv = p.dv, dkp = KP * RPT;
+  float2* fq = reinterpret_cast<float2*>(smem);            // [TCH][dkp]  (gate, activated query)
+  float* vv = smem + 2 * TCH * dkp;                        // [TCH][dvp]
+  float* op = vv + TCH * dvp;                              // [TCH][KP][dvp]
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  const int j = tid % dvp, kp = tid / dvp;
+  const bool live = j < dv;
+  const T* qp = (const T*)p.q + h * dk;
+  const T* fp = (const T*)p.f + h * dk;
+  const T* vp = (const T*)p.v + h * dv;
+  const bf16* fb = (const bf16*)p.f_bias + h * dk;
+  const bf16* lo = (const bf16*)p.lower + h * dk;
+  const bf16* nw = (const bf16*)p.norm_w;
+  float* Sg = p.state ? p.state + ((int64_t)b * p.H + h) * dk * (int64_t)dv : nullptr;
+
+  float S[RPT];
+#pragma unroll
+  for (int r = 0; r < RPT; ++r) {
+    const int k = kp * RPT + r;
+    S[r] = (Sg && !p.zero_start && live && k < dk) ? Sg[(int64_t)k * dv + j] : 0.f;
+  }
+
+  for (int64_t t0 = 0; t0 < p.L; t0 += TCH) {
+    const int nt = (int)min((int64_t)TCH, p.L - t0);
+    const int64_t row0 = (int64_t)b * p.L + t0;
+    __syncthreads();                                   // the previous round's read-outs have been folded
+    for (int i = tid; i < nt * dkp; i += nthr) {
+      const int tt = i / dkp, k = i % dkp;
+      float2 e = make_float2(0.f, 0.f);
+      if (k < dk) {
+        const float l = __bfloat162float(lo[k]);
+        const float fr = ldf(fp + (row0 + tt) * p.ld + k) + __bfloat162float(fb[k]);
+        const float qr = ldf(qp + (row0 + tt) * p.ld + k);
+        e.x = l + (1.f - l) / (1.f + expf(-fr));
+        e.y = qr / (1.f + expf(-qr));
+      }
+      fq[i] = e;
+    }
+    for (int i = tid; i < nt * dvp; i += nthr) {
+      const int tt = i / dvp, c = i % dvp;
+      vv[i] = c < dv ? ldf(vp + (row0 + tt) * p.ld + c) : 0.f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float v = vv[tt * dvp + j];
+      const float2* e = fq + tt * dkp + kp * RPT;
+      float o = 0.f;
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) {
+        const float2 g = e[r];
+        S[r] = fmaf(g.x, S[r] - v, v);                 // g S + (1 - g) v
+        o = fmaf(S[r], g.y, o);
+      }
+      op[(tt * KP + kp) * dvp + j] = o;
+    }
+    __syncthreads();
+    // fold the row groups, norm over the head's dv values, store: one warp per token
+    for (int tt = tid >> 5; tt < nt; tt += nthr >> 5) {
+      const int lane = tid & 31;
+      float ss = 0.f;
+      for (int c = lane; c < dv; c += 32) {
+        float o = 0.f;
+        for (int q = 0; q < KP; ++q) o += op[(tt * KP + q) * dvp + c];
+        op[(tt * KP) * dvp + c] = o;                   // this lane re-reads its own columns below
+        ss = fmaf(o, o, ss);
+      }
+#pragma unroll
+      for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+      const float rstd = 1.0f / sqrtf(ss / (float)dv + p.eps);
+      T* orow = (T*)p.out + (row0 + tt) * p.ldo;
+      for (int c = lane; c < dv; c += 32) stf(orow + h * dv + c, op[(tt * KP) * dvp + c] * rstd * __bfloat162float(nw[c]));
+      if (h == p.H - 1)
+        for (int64_t c = (int64_t)p.H * dv + lane; c < p.ldo; c += 32) stf(orow + c, 0.f);
+    }
+  }
+  if (Sg && live) {
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) {
+      const int k = kp * RPT + r;
+      if (k < dk) Sg[(int64_t)k * dv + j] = S[r];
+    }
+  }
+}
+
+template <typename T, int RPT>
+int launch(const evo_hgrn2_params* p, int KP, int dvp, cudaStream_t st) {
+  const size_t smem = sizeof(float) * ((size_t)2 * TCH * KP * RPT + (size_t)TCH * dvp + (size_t)TCH * KP * dvp);
+  auto kern = hgrn2_kernel<T, RPT>;
+  if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<dim3(p->H, p->B), dim3(KP * dvp), smem, st>>>(*p, KP, dvp);
+  return check_launch("evo_hgrn2_fwd");
+}
+
+template <typename T>
+int dispatch(const evo_hgrn2_params* p, cudaStream_t st) {
+  const int dvp = (p->dv + 31) / 32 * 32;
+  // fewest state rows per thread that still fit one CTA: more threads hide the shared-memory latency of the time loop
+  for (int rpt : {8, 16, 32, 64}) {
+    const int KP = (p->dk + rpt - 1) / rpt;
+    if ((int64_t)KP * dvp > (rpt <= 16 ? 1024 : (rpt == 32 ? 512 : 256))) continue;      // register budget: rpt state rows per thread
+    if (rpt == 8) return launch<T, 8>(p, KP, dvp, st);
+    if (rpt == 16) return launch<T, 16>(p, KP, dvp, st);
+    if (rpt == 32) return launch<T, 32>(p, KP, dvp, st);
+    return launch<T, 64>(p, KP, dvp, st);
+  }
+  set_error("evo_hgrn2_fwd: a head of %d x %d state does not fit one CTA (dk/64 * dv must be <= 256)", p->dk, p->dv);
+  return -1;
+}
+
+}  // namespace
+
+extern "C" int evo_hgrn2_fwd(const evo_hgrn2_params* p, void* stream) {
+  EVO_REQUIRE(p->q && p->f && p->v && p->f_bias && p->lower && p->norm_w && p->out, "evo_hgrn2_fwd: null argument");
+  EVO_REQUIRE(p->B >= 0 && p->L >= 0 && p->H > 0 && p->dk > 0 && p->dv > 0 && p->ldo >= (int64_t)p->H * p->dv, "evo_hgrn2_fwd: bad shape");
+  if (p->B == 0 || p->L == 0) return 0;
+  return p->dtype ? dispatch<float>(p, (cudaStream_t)stream) : dispatch<bf16>(p, (cudaStream_t)stream);
+}

@@ -1,0 +1,233 @@
+// Row-wise kernels for models that keep the residual stream in fp32: embedding gather into fp32, residual update +
+// RMS norm in one pass (with an optional halo of carried rows for a short causal convolution that follows), the
+// per-channel causal convolution itself, the PolyNorm activation, the tanh soft cap of the logits and a strided row copy
+// (cache append).  Activations that feed a GEMM are written in the GEMM's input type (bf16, or fp32 for the all-fp32
+// mode) with the pad columns [D, ld) zero-filled, so that K can be padded to the tensor-core tile without a second pass.
+// All statistics (mean squares, reciprocal roots, polynomial terms, tanh) are fp32.
+#include "common.cuh"
+#include "../../include/evo_b200.h"
+
+using namespace evo;
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// sum over the block (blockDim.x <= 1024, a multiple of 32); every thread gets the total
+__device__ __forceinline__ float block_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();                      // red may still be read from a previous call
+  if ((threadIdx.x & 31) == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+
+// ------------------------------------------------------------------ embedding gather into the fp32 stream
+template <typename IdT>
+__global__ void embed_f32_kernel(const IdT* __restrict__ ids, const bf16* __restrict__ table, float* __restrict__ out,
+                                 int64_t n_tokens, int D, int vocab) {
+  const int64_t row = blockIdx.x;
+  long long id = (long long)ids[row];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  const bf16* src = table + (int64_t)id * D;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) out[row * D + c] = __bfloat162float(src[c]);
+}
+
+// ------------------------------------------------------------------ residual update + RMS norm
+// One CTA per output row.  Output rows are laid out (B, halo + L, .): rows t < halo of a sequence are copies of carried
+// rows (or zeros); the others are norm(x_row) with x_row <- x_row + y_scale * y_row + add_row written back first.
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(256) resid_norm_kernel(evo_resid_norm_params p) {
+  __shared__ float red[32];
+  const int64_t per = p.halo + p.seq_len;
+  const int64_t r = blockIdx.x;
+  const int64_t b = r / per, t = r % per - p.halo;
+  TO* orow = (TO*)p.out + r * p.ldo;
+  const int D = p.D;
+  if (t < 0) {
+    const float* src = p.halo_src ? p.halo_src + (b * p.halo + (t + p.halo)) * (int64_t)D : nullptr;
+    for (int c = threadIdx.x; c < p.ldo; c += blockDim.x) stf(orow + c, (src && c < D) ? src[c] : 0.f);
+    return;
+  }
+  const int64_t srow = p.gather ? p.gather[b * p.seq_len + t] : b * p.seq_len + t;
+  float* xr = p.x + srow * D;
+  const TY* yr = p.y ? (const TY*)p.y + srow * p.ldy : nullptr;
+  const float* ar = p.x_add ? p.x_add + srow * D : nullptr;
+  const bool update = (yr != nullptr || ar != nullptr) && p.gather == nullptr;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    float v = xr[c];
+    if (yr) v = fmaf(p.y_scale, ldf(yr + c), v);
+    if (ar) v += ar[c];
+    if (update) xr[c] = v;
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, red);
+  const float rstd = 1.0f / sqrtf(ss / (float)D + p.eps);
+  const bf16* w = (const bf16*)p.weight;
+  for (int c = threadIdx.x; c < p.ldo; c += blockDim.x) {
+    float h = 0.f;
+    if (c < D) {
+      float v = xr[c];
+      if (!update) {                      // nothing was written back: rebuild the value
+        if (yr) v = fmaf(p.y_scale, ldf(yr + c), v);
+        if (ar) v += ar[c];
+      }
+      h = v * rstd;
+      if (w) h *= p.weight_offset + __bfloat162float(w[c]);
+    }
+    stf(orow + c, h);
+  }
+}
+
+// ------------------------------------------------------------------ per-channel causal convolution with a skip path
+// in (B, taps-1 + L, D) fp32: the first taps-1 rows of a sequence are the carried inputs.  out[b,t,c] = in[b,taps-1+t,c] +
+// sum_j w[c,j] * in[b,t+j,c]; the last taps-1 input rows become the next carried rows.
+template <typename TO>
+__global__ void __launch_bounds__(256) causal_conv_kernel(evo_causal_conv_params p) {
+  const int halo = p.taps - 1;
+  const int64_t per = p.seq_len + halo;
+  const int64_t r = blockIdx.x;
+  const int64_t b = r / per, t = r % per;
+  const float* in = p.in + b * per * (int64_t)p.D;
+  const bf16* w = (const bf16*)p.weight;
+  if (t >= p.seq_len) {                   // carried rows for the next call
+    if (!p.carry_out) return;
+    const int64_t k = t - p.seq_len;
+    for (int c = threadIdx.x; c < p.D; c += blockDim.x) p.carry_out[(b * halo + k) * (int64_t)p.D + c] = in[(p.seq_len + k) * (int64_t)p.D + c];
+    return;
+  }
+  TO* orow = (TO*)p.out + (b * p.seq_len + t) * p.ldo;
+  for (int c = threadIdx.x; c < p.ldo; c += blockDim.x) {
+    float acc = 0.f;
+    if (c < p.D) {
+      acc = in[(t + halo) * (int64_t)p.D + c];
+      for (int j = 0; j < p.taps; ++j) acc = fmaf(__bfloat162float(w[(int64_t)c * p.taps + j]), in[(t + j) * (int64_t)p.D + c], acc);
+    }
+    stf(orow + c, acc);
+  }
+}
+
+// ------------------------------------------------------------------ PolyNorm: a N(z) + b N(z^2) + c N(z^3) + e
+// N divides a row by its root mean square; one CTA per row, two passes over the row (the second one hits L1/L2).
+template <typename T>
+__global__ void __launch_bounds__(256) polynorm_kernel(const T* __restrict__ z, int64_t ldz, const bf16* __restrict__ coef, T* __restrict__ out,
+                                                       int64_t ldo, int F, float eps) {
+  __shared__ float red[32];
+  const T* zr = z + (int64_t)blockIdx.x * ldz;
+  T* orow = out + (int64_t)blockIdx.x * ldo;
+  float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  for (int c = threadIdx.x; c < F; c += blockDim.x) {
+    const float v = ldf(zr + c), v2 = v * v, v3 = v2 * v;
+    s1 = fmaf(v, v, s1); s2 = fmaf(v2, v2, s2); s3 = fmaf(v3, v3, s3);
+  }
+  s1 = block_sum(s1, red); s2 = block_sum(s2, red); s3 = block_sum(s3, red);
+  const float a = __bfloat162float(coef[0]) / sqrtf(s1 / (float)F + eps);
+  const float b = __bfloat162float(coef[1]) / sqrtf(s2 / (float)F + eps);
+  const float c3 = __bfloat162float(coef[2]) / sqrtf(s3 / (float)F + eps);
+  const float e = __bfloat162float(coef[3]);
+  for (int c = threadIdx.x; c < ldo; c += blockDim.x) {
+    float o = 0.f;
+    if (c < F) {
+      const float v = ldf(zr + c), v2 = v * v;
+      o = fmaf(a, v, fmaf(b, v2, fmaf(c3, v2 * v, e)));
+    }
+    stf(orow + c, o);
+  }
+}
+
+template <typename T>
+__global__ void softcap_kernel(const T* __restrict__ in, int64_t ldi, float* __restrict__ out, int64_t rows, int V, float cap) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * V) return;
+  const int64_t r = i / V; const int c = (int)(i % V);
+  const float v = ldf(in + r * ldi + c);
+  out[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+}
+
+// rows of `width` elements from src (row stride lds) to dst rows [pos, pos + L) of each sequence (row stride ldd, batch stride)
+template <typename T>
+__global__ void copy_rows_kernel(const T* __restrict__ src, int64_t lds, T* __restrict__ dst, int64_t ldd, int64_t dst_batch_stride,
+                                 int B, int64_t L, int width, int64_t pos0, const long long* __restrict__ pos_dev) {
+  const int64_t r = blockIdx.x;
+  const int64_t b = r / L, t = r % L;
+  const int64_t pos = (pos_dev ? (int64_t)*pos_dev : pos0) + t;
+  const T* s = src + r * lds;
+  T* d = dst + b * dst_batch_stride + pos * ldd;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) d[c] = s[c];
+}
+
+}  // namespace
+
+extern "C" int evo_embed_f32(const void* ids, int ids_are_i64, const void* table, float* out, int64_t n_tokens, int D, int vocab, void* stream) {
+  if (n_tokens == 0) return 0;
+  dim3 grid((unsigned)n_tokens), block(128);
+  if (ids_are_i64) embed_f32_kernel<long long><<<grid, block, 0, (cudaStream_t)stream>>>((const long long*)ids, (const bf16*)table, out, n_tokens, D, vocab);
+  else embed_f32_kernel<int><<<grid, block, 0, (cudaStream_t)stream>>>((const int*)ids, (const bf16*)table, out, n_tokens, D, vocab);
+  return check_launch("evo_embed_f32");
+}
+
+extern "C" int evo_resid_norm(const evo_resid_norm_params* p, void* stream) {
+  EVO_REQUIRE(p->x && p->out && p->D > 0 && p->ldo >= p->D && p->B >= 0 && p->seq_len >= 0 && p->halo >= 0, "evo_resid_norm: bad arguments");
+  EVO_REQUIRE(p->y == nullptr || p->ldy >= p->D, "evo_resid_norm: ldy < D");
+  const int64_t rows = (int64_t)p->B * (p->halo + p->seq_len);
+  if (rows == 0 || p->seq_len == 0) return 0;
+  dim3 grid((unsigned)rows), block(p->D >= 1024 ? 256 : 128);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int key = (p->y_dtype ? 2 : 0) | (p->out_dtype ? 1 : 0);
+  switch (key) {
+    case 0: resid_norm_kernel<bf16, bf16><<<grid, block, 0, st>>>(*p); break;
+    case 1: resid_norm_kernel<bf16, float><<<grid, block, 0, st>>>(*p); break;
+    case 2: resid_norm_kernel<float, bf16><<<grid, block, 0, st>>>(*p); break;
+    default: resid_norm_kernel<float, float><<<grid, block, 0, st>>>(*p); break;
+  }
+  return check_launch("evo_resid_norm");
+}
+
+extern "C" int evo_causal_conv(const evo_causal_conv_params* p, void* stream) {
+  EVO_REQUIRE(p->in && p->out && p->weight && p->D > 0 && p->taps >= 1 && p->ldo >= p->D && p->B >= 0 && p->seq_len >= 0, "evo_causal_conv: bad arguments");
+  const int64_t rows = (int64_t)p->B * (p->seq_len + p->taps - 1);
+  if (rows == 0) return 0;
+  dim3 grid((unsigned)rows), block(p->D >= 1024 ? 256 : 128);
+  if (p->out_dtype) causal_conv_kernel<float><<<grid, block, 0, (cudaStream_t)stream>>>(*p);
+  else causal_conv_kernel<bf16><<<grid, block, 0, (cudaStream_t)stream>>>(*p);
+  return check_launch("evo_causal_conv");
+}
+
+extern "C" int evo_polynorm(const void* z, int64_t ldz, const void* coef, void* out, int64_t ldo, int64_t rows, int F, float eps, int dtype, void* stream) {
+  EVO_REQUIRE(z && out && coef && F > 0 && ldz >= F && ldo >= F, "evo_polynorm: bad arguments");
+  if (rows == 0) return 0;
+  dim3 grid((unsigned)rows), block(256);
+  if (dtype) polynorm_kernel<float><<<grid, block, 0, (cudaStream_t)stream>>>((const float*)z, ldz, (const bf16*)coef, (float*)out, ldo, F, eps);
+  else polynorm_kernel<bf16><<<grid, block, 0, (cudaStream_t)stream>>>((const bf16*)z, ldz, (const bf16*)coef, (bf16*)out, ldo, F, eps);
+  return check_launch("evo_polynorm");
+}
+
+extern "C" int evo_softcap_logits(const void* in, int64_t ldi, float* out, int64_t rows, int V, float cap, int dtype, void* stream) {
+  EVO_REQUIRE(in && out && V > 0 && ldi >= V, "evo_softcap_logits: bad arguments");
+  if (rows == 0) return 0;
+  const int64_t n = rows * V;
+  dim3 grid((unsigned)((n + 255) / 256)), block(256);
+  if (dtype) softcap_kernel<float><<<grid, block, 0, (cudaStream_t)stream>>>((const float*)in, ldi, out, rows, V, cap);
+  else softcap_kernel<bf16><<<grid, block, 0, (cudaStream_t)stream>>>((const bf16*)in, ldi, out, rows, V, cap);
+  return check_launch("evo_softcap_logits");
+}
+
+extern "C" int evo_copy_rows(const void* src, int64_t lds, void* dst, int64_t ldd, int64_t dst_batch_stride, int B, int64_t L, int width,
+                             int64_t pos0, const int64_t* pos_dev, int dtype, void* stream) {
+  EVO_REQUIRE(src && dst && width > 0 && lds >= width && ldd >= width, "evo_copy_rows: bad arguments");
+  if ((int64_t)B * L == 0) return 0;
+  dim3 grid((unsigned)((int64_t)B * L)), block(128);
+  if (dtype) copy_rows_kernel<float><<<grid, block, 0, (cudaStream_t)stream>>>((const float*)src, lds, (float*)dst, ldd, dst_batch_stride, B, L, width, pos0, (const long long*)pos_dev);
+  else copy_rows_kernel<bf16><<<grid, block, 0, (cudaStream_t)stream>>>((const bf16*)src, lds, (bf16*)dst, ldd, dst_batch_stride, B, L, width, pos0, (const long long*)pos_dev);
+  return check_launch("evo_copy_rows");
+}

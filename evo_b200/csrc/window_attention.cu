@@ -1,0 +1,298 @@
+// Softmax attention over a linear key/value cache with (a) a sliding window that also keeps the first tokens of the
+// sequence, (b) one or two score maps per head over the same values (differential attention: o = a1 - lambda * a2),
+// (c) an optional per-head RMS norm without weight and (d) an optional sigmoid output gate -- one fused kernel; the
+// scores, the softmax weights, the combination of the maps and the head norm are fp32 whatever the activation type.
+//
+// Work per query is bounded by window + keep_first keys, so the kernel is a CUDA-core streaming-softmax kernel: one warp
+// per query, 8 consecutive queries per CTA share every 32-key tile of K and V through shared memory (their windows overlap
+// almost completely); lane j scores key j of the tile against both maps, the probabilities are broadcast by shuffle and each
+// lane accumulates dv/32 value channels.  A CTA only walks the tiles of [0, keep_first) and of the union of its windows.
+// With few queries (the single-token step) the warps of a CTA split the key tiles of ONE query instead and merge their
+// partial softmax states through shared memory.
+#include "common.cuh"
+#include "../../include/evo_b200.h"
+#include <math.h>
+
+using namespace evo;
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+constexpr int QT = 8;        // warps per CTA
+constexpr int KT = 32;       // keys per tile (one per lane)
+constexpr int MAXCV = 8;     // value channels per lane: dv <= 256
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <int NM>
+struct Softmax {
+  float m[NM], l[NM], acc[NM][MAXCV];
+  __device__ __forceinline__ void init() {
+#pragma unroll
+    for (int a = 0; a < NM; ++a) {
+      m[a] = -INFINITY; l[a] = 0.f;
+#pragma unroll
+      for (int c = 0; c < MAXCV; ++c) acc[a][c] = 0.f;
+    }
+  }
+};
+
+// scores of this lane's key for all maps -> running max / sum update; returns the lane's probabilities in pm
+template <int NM>
+__device__ __forceinline__ bool tile_scores(Softmax<NM>& sm, const float* qrow, const float* krow, int dk, float scale, bool vis, float* pm) {
+  float s[NM];
+#pragma unroll
+  for (int a = 0; a < NM; ++a) {
+    float d = 0.f;
+    for (int e = 0; e < dk; ++e) d = fmaf(qrow[a * dk + e], krow[a * dk + e], d);
+    s[a] = vis ? d * scale : -INFINITY;
+  }
+  if (!__any_sync(0xffffffffu, vis)) return false;
+#pragma unroll
+  for (int a = 0; a < NM; ++a) {
+    const float mn = fmaxf(sm.m[a], warp_max(s[a]));
+    const float corr = expf(sm.m[a] - mn);
+    pm[a] = vis ? expf(s[a] - mn) : 0.f;
+    sm.l[a] = sm.l[a] * corr + warp_sum(pm[a]);
+    sm.m[a] = mn;
+#pragma unroll
+    for (int c = 0; c < MAXCV; ++c) sm.acc[a][c] *= corr;
+  }
+  return true;
+}
+
+// combination of the maps, head norm, gate, store (one warp = one query row)
+template <typename T, int NM>
+__device__ __forceinline__ void finish_row(const evo_window_attn_params& p, const Softmax<NM>& sm, int64_t row, int h, int lane) {
+  const int dv = p.dv;
+  float o[MAXCV];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < MAXCV; ++c) {
+    float v = sm.acc[0][c] / sm.l[0];
+    if (NM == 2) v -= p.lambda * (sm.acc[NM - 1][c] / sm.l[NM - 1]);
+    o[c] = (lane + 32 * c < dv) ? v : 0.f;
+    ss = fmaf(o[c], o[c], ss);
+  }
+  float mul = 1.f;
+  if (p.head_norm) mul = p.out_scale / sqrtf(warp_sum(ss) / (float)dv + p.norm_eps);
+  T* orow = (T*)p.out + row * p.ldo;
+  const T* grow = p.gate ? (const T*)p.gate + row * p.gate_tok_stride + h * dv : nullptr;
+#pragma unroll
+  for (int c = 0; c < MAXCV; ++c) {
+    const int ch = lane + 32 * c;
+    if (ch < dv) {
+      float v = o[c] * mul;
+      if (grow) v *= 1.f / (1.f + expf(-ldf(grow + ch)));
+      stf(orow + h * dv + ch, v);
+    }
+  }
+  if (h == p.H - 1)
+    for (int64_t c = (int64_t)p.H * dv + lane; c < p.ldo; c += 32) stf(orow + c, 0.f);
+}
+
+// ---- many queries: one warp per query, K/V tiles shared by the CTA's 8 consecutive queries
+template <typename T, int NM>
+__global__ void __launch_bounds__(QT * 32) window_attn_kernel(evo_window_attn_params p) {
+  extern __shared__ float smem[];
+  const int dk = p.dk, dv = p.dv, kw = NM * dk, kst = kw + 1;
+  float* Ks = smem;                       // [KT][kw + 1]
+  float* Vs = Ks + KT * kst;              // [KT][dv]
+  float* Qs = Vs + KT * dv;               // [QT][kw]
+  const int b = blockIdx.z, h = blockIdx.y, g = h / (p.H / p.G);
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t pos = p.pos_dev ? (int64_t)*p.pos_dev : p.q_pos0;
+  const int64_t rel0 = (int64_t)blockIdx.x * QT;
+  const int64_t rel = rel0 + w;
+  const bool valid = rel < p.Lq;
+  const int64_t i = pos + rel;
+  const int64_t row = (int64_t)b * p.Lq + rel;
+  if (valid) {
+    const T* q = (const T*)p.q + row * p.q_tok_stride + (int64_t)h * kw;
+    for (int e = lane; e < kw; e += 32) Qs[w * kw + e] = ldf(q + e);
+  }
+  const T* kb = (const T*)p.k + (int64_t)b * p.k_batch_stride + (int64_t)g * kw;
+  const T* vb = (const T*)p.v + (int64_t)b * p.v_batch_stride + (int64_t)g * dv;
+  const int64_t i_lo = pos + rel0, i_hi = pos + min(p.Lq - 1, rel0 + QT - 1);
+  const bool windowed = p.window > 0;
+  const int64_t win_lo = windowed ? max((int64_t)0, i_lo - p.window + 1) : 0;
+  const int64_t keep_hi = windowed ? min(p.keep_first, win_lo) : 0;
+
+  Softmax<NM> sm;
+  sm.init();
+  for (int part = 0; part < 2; ++part) {
+    const int64_t lo = part == 0 ? 0 : win_lo, hi = part == 0 ? keep_hi : i_hi + 1;       // keys [lo, hi)
+    for (int64_t k0 = lo; k0 < hi; k0 += KT) {
+      const int nk = (int)min((int64_t)KT, hi - k0);
+      __syncthreads();
+      for (int idx = threadIdx.x; idx < nk * kw; idx += QT * 32) {
+        const int r = idx / kw, e = idx % kw;
+        Ks[r * kst + e] = ldf(kb + (k0 + r) * p.k_tok_stride + e);
+      }
+      for (int idx = threadIdx.x; idx < nk * dv; idx += QT * 32) {
+        const int r = idx / dv, e = idx % dv;
+        Vs[r * dv + e] = ldf(vb + (k0 + r) * p.v_tok_stride + e);
+      }
+      __syncthreads();
+      if (!valid) continue;
+      const int64_t kj = k0 + lane;
+      const bool vis = lane < nk && kj <= i && (!windowed || i - kj < p.window || kj < p.keep_first);
+      float pm[NM];
+      if (!tile_scores<NM>(sm, Qs + w * kw, Ks + (lane < nk ? lane : 0) * kst, dk, p.scale, vis, pm)) continue;
+      for (int r = 0; r < nk; ++r) {
+        float pr[NM];
+#pragma unroll
+        for (int a = 0; a < NM; ++a) pr[a] = __shfl_sync(0xffffffffu, pm[a], r);
+#pragma unroll
+        for (int c = 0; c < MAXCV; ++c) {
+          const int ch = lane + 32 * c;
+          if (ch < dv) {
+            const float vv = Vs[r * dv + ch];
+#pragma unroll
+            for (int a = 0; a < NM; ++a) sm.acc[a][c] = fmaf(pr[a], vv, sm.acc[a][c]);
+          }
+        }
+      }
+    }
+  }
+  if (valid) finish_row<T, NM>(p, sm, row, h, lane);
+}
+
+// ---- few queries: one CTA per (query, head); its warps take the key tiles round-robin, straight from global memory
+template <typename T, int NM>
+__global__ void __launch_bounds__(QT * 32) window_attn_split_kernel(evo_window_attn_params p) {
+  extern __shared__ float smem[];
+  const int dk = p.dk, dv = p.dv, kw = NM * dk;
+  float* Qs = smem;                                   // [kw]
+  float* Mg = Qs + kw;                                // [QT][NM][2 + dvp] partial (max, sum, acc)
+  const int dvp = MAXCV * 32;
+  const int b = blockIdx.z, h = blockIdx.y, g = h / (p.H / p.G);
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t pos = p.pos_dev ? (int64_t)*p.pos_dev : p.q_pos0;
+  const int64_t rel = blockIdx.x, i = pos + rel, row = (int64_t)b * p.Lq + rel;
+  const T* q = (const T*)p.q + row * p.q_tok_stride + (int64_t)h * kw;
+  for (int e = threadIdx.x; e < kw; e += QT * 32) Qs[e] = ldf(q + e);
+  __syncthreads();
+  const T* kb = (const T*)p.k + (int64_t)b * p.k_batch_stride + (int64_t)g * kw;
+  const T* vb = (const T*)p.v + (int64_t)b * p.v_batch_stride + (int64_t)g * dv;
+  const bool windowed = p.window > 0;
+  const int64_t win_lo = windowed ? max((int64_t)0, i - p.window + 1) : 0;
+  const int64_t keep_hi = windowed ? min(p.keep_first, win_lo) : 0;
+  const int64_t n_keep = (keep_hi + KT - 1) / KT, n_win = (i + 1 - win_lo + KT - 1) / KT;
+
+  Softmax<NM> sm;
+  sm.init();
+  for (int64_t t = w; t < n_keep + n_win; t += QT) {
+    const int64_t k0 = t < n_keep ? t * KT : win_lo + (t - n_keep) * KT;
+    const int64_t hi = t < n_keep ? keep_hi : i + 1;
+    const int nk = (int)min((int64_t)KT, hi - k0);
+    const bool vis = lane < nk;                        // every key of these ranges is visible to the one query
+    const T* krow = kb + (k0 + (vis ? lane : 0)) * p.k_tok_stride;
+    float s[NM], pm[NM];
+#pragma unroll
+    for (int a = 0; a < NM; ++a) {
+      float d = 0.f;
+      for (int e = 0; e < dk; ++e) d = fmaf(Qs[a * dk + e], ldf(krow + a * dk + e), d);
+      s[a] = vis ? d * p.scale : -INFINITY;
+    }
+#pragma unroll
+    for (int a = 0; a < NM; ++a) {
+      const float mn = fmaxf(sm.m[a], warp_max(s[a]));
+      const float corr = expf(sm.m[a] - mn);
+      pm[a] = vis ? expf(s[a] - mn) : 0.f;
+      sm.l[a] = sm.l[a] * corr + warp_sum(pm[a]);
+      sm.m[a] = mn;
+#pragma unroll
+      for (int c = 0; c < MAXCV; ++c) sm.acc[a][c] *= corr;
+    }
+    for (int r = 0; r < nk; ++r) {
+      float pr[NM];
+#pragma unroll
+      for (int a = 0; a < NM; ++a) pr[a] = __shfl_sync(0xffffffffu, pm[a], r);
+      const T* vrow = vb + (k0 + r) * p.v_tok_stride;
+#pragma unroll
+      for (int c = 0; c < MAXCV; ++c) {
+        const int ch = lane + 32 * c;
+        if (ch < dv) {
+          const float vv = ldf(vrow + ch);
+#pragma unroll
+          for (int a = 0; a < NM; ++a) sm.acc[a][c] = fmaf(pr[a], vv, sm.acc[a][c]);
+        }
+      }
+    }
+  }
+  // merge the warps' partial states in warp 0
+#pragma unroll
+  for (int a = 0; a < NM; ++a) {
+    float* dst = Mg + ((w * NM + a) * (2 + dvp));
+    if (lane == 0) { dst[0] = sm.m[a]; dst[1] = sm.l[a]; }
+#pragma unroll
+    for (int c = 0; c < MAXCV; ++c) dst[2 + lane + 32 * c] = sm.acc[a][c];
+  }
+  __syncthreads();
+  if (w != 0) return;
+  Softmax<NM> tot;
+  tot.init();
+#pragma unroll
+  for (int a = 0; a < NM; ++a) {
+    float mx = -INFINITY;
+    for (int ww = 0; ww < QT; ++ww) mx = fmaxf(mx, Mg[(ww * NM + a) * (2 + dvp)]);
+    tot.m[a] = mx;
+    for (int ww = 0; ww < QT; ++ww) {
+      const float* src = Mg + (ww * NM + a) * (2 + dvp);
+      if (src[0] == -INFINITY) continue;              // this warp saw no tile
+      const float sc = expf(src[0] - mx);
+      tot.l[a] = fmaf(src[1], sc, tot.l[a]);
+#pragma unroll
+      for (int c = 0; c < MAXCV; ++c) tot.acc[a][c] = fmaf(src[2 + lane + 32 * c], sc, tot.acc[a][c]);
+    }
+  }
+  finish_row<T, NM>(p, tot, row, h, lane);
+}
+
+template <typename T, int NM>
+int launch(const evo_window_attn_params* p, cudaStream_t st) {
+  const int kw = NM * p->dk;
+  if (p->Lq <= 4) {
+    const size_t smem = sizeof(float) * ((size_t)kw + (size_t)QT * NM * (2 + MAXCV * 32));
+    auto kern = window_attn_split_kernel<T, NM>;
+    if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<dim3((unsigned)p->Lq, p->H, p->B), QT * 32, smem, st>>>(*p);
+  } else {
+    const size_t smem = sizeof(float) * ((size_t)KT * (kw + 1) + (size_t)KT * p->dv + (size_t)QT * kw);
+    EVO_REQUIRE(smem <= 227 * 1024, "evo_window_attn_fwd: head too wide for shared memory (%zu bytes)", smem);
+    auto kern = window_attn_kernel<T, NM>;
+    if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<dim3((unsigned)((p->Lq + QT - 1) / QT), p->H, p->B), QT * 32, smem, st>>>(*p);
+  }
+  return check_launch("evo_window_attn_fwd");
+}
+
+}  // namespace
+
+extern "C" int evo_window_attn_fwd(const evo_window_attn_params* p, void* stream) {
+  EVO_REQUIRE(p->q && p->k && p->v && p->out, "evo_window_attn_fwd: null argument");
+  EVO_REQUIRE(p->B >= 0 && p->Lq >= 0 && p->H > 0 && p->G > 0 && p->H % p->G == 0 && p->dk > 0 && p->dv > 0, "evo_window_attn_fwd: bad shape");
+  EVO_REQUIRE(p->n_maps == 1 || p->n_maps == 2, "evo_window_attn_fwd: n_maps must be 1 or 2");
+  EVO_REQUIRE(p->dv <= MAXCV * 32, "evo_window_attn_fwd: dv (%d) must be <= %d", p->dv, MAXCV * 32);
+  EVO_REQUIRE(p->ldo >= (int64_t)p->H * p->dv, "evo_window_attn_fwd: ldo too small");
+  if (p->B == 0 || p->Lq == 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (p->dtype) return p->n_maps == 2 ? launch<float, 2>(p, st) : launch<float, 1>(p, st);
+  return p->n_maps == 2 ? launch<bf16, 2>(p, st) : launch<bf16, 1>(p, st);
+}

@@ -186,3 +186,33 @@ def load_streaming(model, model_dir: str, device) -> Dict[str, int]:
     if device.type == "cuda":
         torch.cuda.synchronize(device)
     return {"tensors": len(seen), "bytes": nbytes}
+
+
+def load_named_tensors(model_dir: str, device, shapes: Dict[str, tuple], what: str = "model"):
+    """Flat-named checkpoints (one tensor per name, no module tree): every tensor goes mmap -> pinned staging -> device and is
+    checked against `shapes` with the strict-mode rules of load_streaming.  Returns ({name: device tensor}, stats)."""
+    device = torch.device(device)
+    stage = _Staging(device)
+    out, unexpected, errors, nbytes = {}, [], [], 0
+    for path in shard_files(model_dir):
+        for name, dt, shape, raw in iter_safetensors(path):
+            if name not in shapes:
+                unexpected.append(name)
+                continue
+            if tuple(shape) != tuple(shapes[name]):
+                errors.append(f"size mismatch for {name}: checkpoint {tuple(shape)}, model {tuple(shapes[name])}")
+                continue
+            out[name] = stage.to_device(raw, dt, shape).clone() if device.type != "cuda" else stage.to_device(raw, dt, shape)
+            nbytes += len(raw)
+    missing = [k for k in shapes if k not in out]
+    if missing or unexpected or errors:
+        msg = [f"Error(s) in loading state_dict for {what}:"]
+        if missing:
+            msg.append("\tMissing key(s) in state_dict: " + ", ".join(f'"{k}"' for k in missing) + ".")
+        if unexpected:
+            msg.append("\tUnexpected key(s) in state_dict: " + ", ".join(f'"{k}"' for k in unexpected) + ".")
+        msg.extend("\t" + e for e in errors)
+        raise RuntimeError("\n".join(msg))
+    if device.type == "cuda":
+        torch.cuda.synchronize(device)
+    return out, {"tensors": len(out), "bytes": nbytes}

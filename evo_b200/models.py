@@ -97,6 +97,52 @@ def load_checkpoint(model_name: str = "evo-1-8k-base", config_path: Optional[str
     return model
 
 
+def _load_zaverax(model_dir: str, config: dict, device, dtype, **kwargs):
+    from .ingest import load_named_tensors
+    from .zaverax import Zaverax, ZaveraxConfig
+    model = Zaverax(ZaveraxConfig.from_dict(config), dtype=dtype or torch.bfloat16)
+    dev = torch.device(device) if device is not None else torch.device("cpu")
+    shapes = {k: tuple(v.shape) for k, v in model.weights.items()}
+    tensors, model.ingest_stats = load_named_tensors(model_dir, dev, shapes, type(model).__name__)
+    for name, t in tensors.items():
+        model.weights[name] = t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16)
+    model._invalidate()
+    return model
+
+
+def _load_stripedhyena(model_dir: str, config: dict, device, dtype, model_name: str = "evo-1-8k-base", **kwargs):
+    if dtype not in (None, torch.bfloat16):
+        raise NotImplementedError("StripedHyena runs in bfloat16 (fp32 poles and residues) only")
+    return load_checkpoint(model_name=model_name, device=device, model_dir=model_dir, **kwargs)
+
+
+# config.json "architecture" -> (loader, activation dtypes the model class can run in)
+ARCHITECTURES = {
+    "Zaverax": (_load_zaverax, (torch.bfloat16, torch.float32)),
+    "StripedHyena": (_load_stripedhyena, (torch.bfloat16,)),
+    "StripedHyenaModelForCausalLM": (_load_stripedhyena, (torch.bfloat16,)),
+}
+
+
+def read_architecture(model_dir: str):
+    """(architecture name, config dict) of a checkpoint folder; the name selects the model class."""
+    with open(os.path.join(model_dir, "config.json")) as f:
+        config = json.load(f)
+    arch = config.get("architecture") or (config.get("architectures") or [None])[0]
+    if arch not in ARCHITECTURES:
+        raise ValueError(f"{model_dir}: architecture {arch!r} is not one of {sorted(ARCHITECTURES)}")
+    return arch, config
+
+
+def load_model_dir(model_dir: str, device: str = None, dtype: Optional[torch.dtype] = None, **kwargs):
+    """Checkpoint folder (config.json + safetensors) -> model on `device`; the model class is chosen by config.json."""
+    arch, config = read_architecture(model_dir)
+    loader, dtypes = ARCHITECTURES[arch]
+    if dtype is not None and dtype not in dtypes:
+        raise NotImplementedError(f"{arch} does not run in {dtype}")
+    return loader(model_dir, config, device, dtype, **kwargs)
+
+
 class Evo:
     """Evo('evo-1-8k-base') -> .model (StripedHyena protocol), .tokenizer."""
 

@@ -275,6 +275,89 @@ typedef struct {
 size_t evo_unembed_score_workspace(int64_t M, int V);
 int evo_unembed_score(const evo_score_params* p, void* stream);
 
+/* ==== models with an fp32 residual stream (Zaverax): row kernels, gated linear recurrence, windowed multi-map attention,
+ * and an all-fp32 linear layer.  `dtype` arguments: 0 = bf16 activations, 1 = fp32 activations (the all-fp32 mode).
+ * Weights and small parameter vectors are always bf16 as stored in the checkpoint. ==== */
+
+/* table (vocab, D) bf16 -> out (n, D) fp32 */
+int evo_embed_f32(const void* ids, int ids_are_i64, const void* table, float* out, int64_t n_tokens, int D, int vocab, void* stream);
+
+/* Residual update + RMS norm in one pass over a row:
+ *   x_row <- x_row + y_scale * y_row + add_row   (fp32, written back when y or x_add is given and gather is NULL)
+ *   out_row = x_row / sqrt(mean(x_row^2) + eps) * (weight_offset + weight)        (weight NULL: no weight)
+ * Output rows are laid out (B, halo + seq_len, ldo): the first `halo` rows of each sequence are copies of halo_src
+ * (B, halo, D) fp32 (zeros when NULL) -- the carried inputs of a causal convolution that reads this output.
+ * gather (B*seq_len) int64: read row gather[i] instead of row i (no write-back); used to norm only the rows whose logits are wanted.
+ * Pad columns [D, ldo) of out are zero-filled. */
+typedef struct {
+  float* x;
+  const void* y; int64_t ldy; int y_dtype; float y_scale;
+  const float* x_add;
+  const void* weight; float weight_offset; float eps;
+  void* out; int64_t ldo; int out_dtype;
+  int B; int64_t seq_len; int64_t halo; int D;
+  const float* halo_src;
+  const int64_t* gather;
+} evo_resid_norm_params;
+int evo_resid_norm(const evo_resid_norm_params* p, void* stream);
+
+/* Per-channel causal convolution over time with a skip path: in (B, taps-1 + seq_len, D) fp32 whose first taps-1 rows are the
+ * carried inputs; out[b,t,:] = in[b,taps-1+t,:] + sum_j weight[:,j] * in[b,t+j,:]; weight (D, taps) bf16.
+ * carry_out (B, taps-1, D) fp32 (optional) receives the last taps-1 input rows. */
+typedef struct {
+  const float* in; const void* weight;
+  void* out; int64_t ldo; int out_dtype;
+  float* carry_out;
+  int B; int64_t seq_len; int D; int taps;
+} evo_causal_conv_params;
+int evo_causal_conv(const evo_causal_conv_params* p, void* stream);
+
+/* PolyNorm: out = a N(z) + b N(z^2) + c N(z^3) + e, N(u) = u / sqrt(mean(u^2) + eps) per row; coef = (a, b, c, e) bf16. */
+int evo_polynorm(const void* z, int64_t ldz, const void* coef, void* out, int64_t ldo, int64_t rows, int F, float eps, int dtype, void* stream);
+/* out (rows, V) fp32 = cap * tanh(in / cap)  (cap <= 0: plain copy) */
+int evo_softcap_logits(const void* in, int64_t ldi, float* out, int64_t rows, int V, float cap, int dtype, void* stream);
+/* rows of `width` elements: src row b*L + t -> dst + b*dst_batch_stride + (pos + t)*ldd, pos = *pos_dev if given else pos0 */
+int evo_copy_rows(const void* src, int64_t lds, void* dst, int64_t ldd, int64_t dst_batch_stride, int B, int64_t L, int width,
+                  int64_t pos0, const int64_t* pos_dev, int dtype, void* stream);
+
+/* Gated linear recurrence (HGRN2): per head, with the raw projections q, f, v of a row,
+ *   qa = silu(q), g = lower + (1 - lower) * sigmoid(f + f_bias),  S <- diag(g) S + (1 - g) v^T,  o = S^T qa,
+ *   out = o / sqrt(mean(o^2) + eps) * norm_w   over the head's dv values.
+ * S (B, H, dk, dv) fp32 is read (unless zero_start) and written back (unless NULL).  q/f/v may point into one fused buffer (row stride ld). */
+typedef struct {
+  const void* q; const void* f; const void* v; int64_t ld;
+  const void* f_bias; const void* lower; const void* norm_w;
+  float eps;
+  float* state; int zero_start;
+  void* out; int64_t ldo; int dtype;
+  int B; int64_t L; int H, dk, dv;
+} evo_hgrn2_params;
+int evo_hgrn2_fwd(const evo_hgrn2_params* p, void* stream);
+
+/* Softmax attention over a linear key/value cache with a sliding window that keeps the first tokens, n_maps (1 or 2) score
+ * maps per head over the same values (differential attention: o = a1 - lambda * a2), an optional per-head RMS norm without
+ * weight times out_scale, and an optional sigmoid gate on the output.
+ *   query row i of a sequence sits at position pos + i (pos = *pos_dev if given, else q_pos0) and sees key j iff
+ *   j <= pos + i and (pos + i - j < window or j < keep_first); window <= 0 means plain causal.
+ *   q: head h, map m at columns (h*n_maps + m)*dk; k: kv head g, map m at (g*n_maps + m)*dk; v: kv head g at g*dv;
+ *   query head h reads kv head h / (H/G).  Scores, softmax weights and the combination are fp32. */
+typedef struct {
+  const void* q; int64_t q_tok_stride;
+  const void* k; const void* v; int64_t k_tok_stride, v_tok_stride, k_batch_stride, v_batch_stride;
+  const void* gate; int64_t gate_tok_stride;
+  void* out; int64_t ldo; int dtype;
+  int B; int64_t Lq; int H, G, dk, dv, n_maps;
+  int64_t q_pos0; const int64_t* pos_dev;
+  int64_t window, keep_first;
+  float scale, lambda;
+  int head_norm; float norm_eps, out_scale;
+} evo_window_attn_params;
+int evo_window_attn_fwd(const evo_window_attn_params* p, void* stream);
+
+/* C (M, N) = A (M, K) . W (N, K)^T with fp32 multiply-add on the CUDA cores (no tensor-core rounding): the linear layer of the
+ * all-fp32 mode, and a shape-agnostic comparator for the bf16 one.  A and C have `dtype`; W is bf16. */
+int evo_gemm_simt(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
