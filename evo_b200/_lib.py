@@ -140,7 +140,8 @@ SIGNATURES = {
     "evo_polynorm": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_float, C.c_int, C.c_void_p]),
     "evo_softcap_logits": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_int, C.c_void_p]),
     "evo_copy_rows": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_int64, C.c_int, C.c_int64, C.c_void_p, C.c_int, C.c_void_p]),
-    "evo_hgrn2_fwd": (C.c_int, [C.POINTER(Hgrn2Params), C.c_void_p]),
+    "evo_hgrn2_workspace": (C.c_size_t, [C.POINTER(Hgrn2Params)]),
+    "evo_hgrn2_fwd": (C.c_int, [C.POINTER(Hgrn2Params), C.c_void_p, C.c_size_t, C.c_void_p]),
     "evo_window_attn_fwd": (C.c_int, [C.POINTER(WindowAttnParams), C.c_void_p]),
     "evo_gemm_simt": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
 }

@@ -7,6 +7,8 @@
 // S[kp*RPT .. kp*RPT+RPT) [j]; 16 tokens of activated gates / queries / values are staged in shared memory per round, so the
 // time loop runs without barriers; partial read-outs of the dk/RPT row groups are folded after each round.
 // The same kernel serves the single-token step (L == 1): the state is then streamed through once.
+// Value channels are independent in the recurrence, so a head whose state does not fit one CTA's registers is split over
+// several CTAs by value channel; the read-outs then go to an fp32 workspace and a second small kernel applies the head norm.
 #include "common.cuh"
 #include "../../include/evo_b200.h"
 
@@ -24,7 +26,7 @@ template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = _
 constexpr int TCH = 16;      // tokens staged per round
 
 template <typename T, int RPT>
-__global__ void __launch_bounds__(RPT <= 16 ? 1024 : (RPT == 32 ? 512 : 256)) hgrn2_kernel(evo_hgrn2_params p, int KP, int dvp) {
+__global__ void __launch_bounds__(RPT <= 16 ? 1024 : (RPT == 32 ? 512 : 256)) hgrn2_kernel(evo_hgrn2_params p, int KP, int dvp, float* __restrict__ raw) {
   extern __shared__ float smem[];
   const int dk = p.dk, dv = p.dv, dkp = KP * RPT;
   float2* fq = reinterpret_cast<float2*>(smem);            // [TCH][dkp]  (gate, activated query)
@@ -32,7 +34,8 @@ __global__ void __launch_bounds__(RPT <= 16 ? 1024 : (RPT == 32 ? 512 : 256)) hg
   float* op = vv + TCH * dvp;                              // [TCH][KP][dvp]
   const int h = blockIdx.x, b = blockIdx.y;
   const int tid = threadIdx.x, nthr = blockDim.x;
-  const int j = tid % dvp, kp = tid / dvp;
+  const int j0 = blockIdx.z * dvp;                         // first value channel of this CTA
+  const int j = j0 + tid % dvp, kp = tid / dvp;
   const bool live = j < dv;
   const T* qp = (const T*)p.q + h * dk;
   const T* fp = (const T*)p.f + h * dk;
@@ -67,11 +70,11 @@ __global__ void __launch_bounds__(RPT <= 16 ? 1024 : (RPT == 32 ? 512 : 256)) hg
     }
     for (int i = tid; i < nt * dvp; i += nthr) {
       const int tt = i / dvp, c = i % dvp;
-      vv[i] = c < dv ? ldf(vp + (row0 + tt) * p.ld + c) : 0.f;
+      vv[i] = j0 + c < dv ? ldf(vp + (row0 + tt) * p.ld + j0 + c) : 0.f;
     }
     __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
-      const float v = vv[tt * dvp + j];
+      const float v = vv[tt * dvp + (j - j0)];
       const float2* e = fq + tt * dkp + kp * RPT;
       float o = 0.f;
 #pragma unroll
@@ -80,12 +83,20 @@ __global__ void __launch_bounds__(RPT <= 16 ? 1024 : (RPT == 32 ? 512 : 256)) hg
         S[r] = fmaf(g.x, S[r] - v, v);                 // g S + (1 - g) v
         o = fmaf(S[r], g.y, o);
       }
-      op[(tt * KP + kp) * dvp + j] = o;
+      op[(tt * KP + kp) * dvp + (j - j0)] = o;
     }
     __syncthreads();
     // fold the row groups, norm over the head's dv values, store: one warp per token
     for (int tt = tid >> 5; tt < nt; tt += nthr >> 5) {
       const int lane = tid & 31;
+      if (raw) {                                       // split head: un-normed read-outs, the norm follows in head_norm_kernel
+        for (int c = lane; c < dvp && j0 + c < dv; c += 32) {
+          float o = 0.f;
+          for (int q = 0; q < KP; ++q) o += op[(tt * KP + q) * dvp + c];
+          raw[((row0 + tt) * p.H + h) * dv + j0 + c] = o;
+        }
+        continue;
+      }
       float ss = 0.f;
       for (int c = lane; c < dv; c += 32) {
         float o = 0.f;
@@ -111,36 +122,80 @@ __global__ void __launch_bounds__(RPT <= 16 ? 1024 : (RPT == 32 ? 512 : 256)) hg
   }
 }
 
+// second pass of a split head: out = raw / sqrt(mean(raw^2) + eps) * norm_w, one warp per (row, head)
+template <typename T>
+__global__ void head_norm_kernel(evo_hgrn2_params p, const float* __restrict__ raw) {
+  const int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (int64_t)p.B * p.L * p.H) return;
+  const int64_t row = wid / p.H; const int h = (int)(wid % p.H);
+  const float* r = raw + wid * p.dv;
+  float ss = 0.f;
+  for (int c = lane; c < p.dv; c += 32) ss = fmaf(r[c], r[c], ss);
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+  const float rstd = 1.0f / sqrtf(ss / (float)p.dv + p.eps);
+  T* orow = (T*)p.out + row * p.ldo;
+  const bf16* nw = (const bf16*)p.norm_w;
+  for (int c = lane; c < p.dv; c += 32) stf(orow + h * p.dv + c, r[c] * rstd * __bfloat162float(nw[c]));
+  if (h == p.H - 1)
+    for (int64_t c = (int64_t)p.H * p.dv + lane; c < p.ldo; c += 32) stf(orow + c, 0.f);
+}
+
+struct Plan { int rpt, KP, dvc, chunks; };
+// fewest state rows per thread that still fit one CTA (more threads hide the shared-memory latency of the time loop);
+// heads too large for that are split by value channel with 64 rows per thread
+inline Plan plan(int dk, int dv) {
+  const int dvp = (dv + 31) / 32 * 32;
+  for (int rpt : {8, 16, 32, 64}) {
+    const int KP = (dk + rpt - 1) / rpt;
+    if ((int64_t)KP * dvp <= (rpt <= 16 ? 1024 : (rpt == 32 ? 512 : 256))) return {rpt, KP, dvp, 1};      // register budget: rpt state rows per thread
+  }
+  const int KP = (dk + 63) / 64;
+  const int dvc = 256 / KP / 32 * 32;
+  if (dvc < 32) return {0, 0, 0, 0};
+  return {64, KP, dvc, (dv + dvc - 1) / dvc};
+}
+
 template <typename T, int RPT>
-int launch(const evo_hgrn2_params* p, int KP, int dvp, cudaStream_t st) {
+int launch(const evo_hgrn2_params* p, int KP, int dvp, int chunks, float* raw, cudaStream_t st) {
   const size_t smem = sizeof(float) * ((size_t)2 * TCH * KP * RPT + (size_t)TCH * dvp + (size_t)TCH * KP * dvp);
   auto kern = hgrn2_kernel<T, RPT>;
   if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<dim3(p->H, p->B), dim3(KP * dvp), smem, st>>>(*p, KP, dvp);
+  kern<<<dim3(p->H, p->B, chunks), dim3(KP * dvp), smem, st>>>(*p, KP, dvp, raw);
+  int rc = check_launch("evo_hgrn2_fwd");
+  if (rc || !raw) return rc;
+  const int64_t warps = (int64_t)p->B * p->L * p->H;
+  head_norm_kernel<T><<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(*p, raw);
   return check_launch("evo_hgrn2_fwd");
 }
 
 template <typename T>
-int dispatch(const evo_hgrn2_params* p, cudaStream_t st) {
-  const int dvp = (p->dv + 31) / 32 * 32;
-  // fewest state rows per thread that still fit one CTA: more threads hide the shared-memory latency of the time loop
-  for (int rpt : {8, 16, 32, 64}) {
-    const int KP = (p->dk + rpt - 1) / rpt;
-    if ((int64_t)KP * dvp > (rpt <= 16 ? 1024 : (rpt == 32 ? 512 : 256))) continue;      // register budget: rpt state rows per thread
-    if (rpt == 8) return launch<T, 8>(p, KP, dvp, st);
-    if (rpt == 16) return launch<T, 16>(p, KP, dvp, st);
-    if (rpt == 32) return launch<T, 32>(p, KP, dvp, st);
-    return launch<T, 64>(p, KP, dvp, st);
+int dispatch(const evo_hgrn2_params* p, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  const Plan pl = plan(p->dk, p->dv);
+  if (pl.rpt == 0) { set_error("evo_hgrn2_fwd: dk (%d) must be <= 512", p->dk); return -1; }
+  float* raw = nullptr;
+  if (pl.chunks > 1) {
+    const size_t need = sizeof(float) * (size_t)p->B * p->L * p->H * p->dv;
+    if (!workspace || workspace_bytes < need) { set_error("evo_hgrn2_fwd: workspace too small (%zu < %zu)", workspace_bytes, need); return -1; }
+    raw = (float*)workspace;
   }
-  set_error("evo_hgrn2_fwd: a head of %d x %d state does not fit one CTA (dk/64 * dv must be <= 256)", p->dk, p->dv);
-  return -1;
+  if (pl.rpt == 8) return launch<T, 8>(p, pl.KP, pl.dvc, pl.chunks, raw, st);
+  if (pl.rpt == 16) return launch<T, 16>(p, pl.KP, pl.dvc, pl.chunks, raw, st);
+  if (pl.rpt == 32) return launch<T, 32>(p, pl.KP, pl.dvc, pl.chunks, raw, st);
+  return launch<T, 64>(p, pl.KP, pl.dvc, pl.chunks, raw, st);
 }
 
 }  // namespace
 
-extern "C" int evo_hgrn2_fwd(const evo_hgrn2_params* p, void* stream) {
+extern "C" size_t evo_hgrn2_workspace(const evo_hgrn2_params* p) {
+  const Plan pl = plan(p->dk, p->dv);
+  return pl.chunks > 1 ? sizeof(float) * (size_t)p->B * p->L * p->H * p->dv : 0;
+}
+
+extern "C" int evo_hgrn2_fwd(const evo_hgrn2_params* p, void* workspace, size_t workspace_bytes, void* stream) {
   EVO_REQUIRE(p->q && p->f && p->v && p->f_bias && p->lower && p->norm_w && p->out, "evo_hgrn2_fwd: null argument");
   EVO_REQUIRE(p->B >= 0 && p->L >= 0 && p->H > 0 && p->dk > 0 && p->dv > 0 && p->ldo >= (int64_t)p->H * p->dv, "evo_hgrn2_fwd: bad shape");
   if (p->B == 0 || p->L == 0) return 0;
-  return p->dtype ? dispatch<float>(p, (cudaStream_t)stream) : dispatch<bf16>(p, (cudaStream_t)stream);
+  return p->dtype ? dispatch<float>(p, workspace, workspace_bytes, (cudaStream_t)stream) : dispatch<bf16>(p, workspace, workspace_bytes, (cudaStream_t)stream);
 }

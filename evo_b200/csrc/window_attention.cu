@@ -26,7 +26,6 @@ template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = _
 
 constexpr int QT = 8;        // warps per CTA
 constexpr int KT = 32;       // keys per tile (one per lane)
-constexpr int MAXCV = 8;     // value channels per lane: dv <= 256
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -39,7 +38,7 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-template <int NM>
+template <int NM, int MAXCV>      // MAXCV: value channels per lane (dv <= 32 * MAXCV)
 struct Softmax {
   float m[NM], l[NM], acc[NM][MAXCV];
   __device__ __forceinline__ void init() {
@@ -53,8 +52,8 @@ struct Softmax {
 };
 
 // scores of this lane's key for all maps -> running max / sum update; returns the lane's probabilities in pm
-template <int NM>
-__device__ __forceinline__ bool tile_scores(Softmax<NM>& sm, const float* qrow, const float* krow, int dk, float scale, bool vis, float* pm) {
+template <int NM, int MAXCV>
+__device__ __forceinline__ bool tile_scores(Softmax<NM, MAXCV>& sm, const float* qrow, const float* krow, int dk, float scale, bool vis, float* pm) {
   float s[NM];
 #pragma unroll
   for (int a = 0; a < NM; ++a) {
@@ -77,8 +76,8 @@ __device__ __forceinline__ bool tile_scores(Softmax<NM>& sm, const float* qrow, 
 }
 
 // combination of the maps, head norm, gate, store (one warp = one query row)
-template <typename T, int NM>
-__device__ __forceinline__ void finish_row(const evo_window_attn_params& p, const Softmax<NM>& sm, int64_t row, int h, int lane) {
+template <typename T, int NM, int MAXCV>
+__device__ __forceinline__ void finish_row(const evo_window_attn_params& p, const Softmax<NM, MAXCV>& sm, int64_t row, int h, int lane) {
   const int dv = p.dv;
   float o[MAXCV];
   float ss = 0.f;
@@ -107,7 +106,7 @@ __device__ __forceinline__ void finish_row(const evo_window_attn_params& p, cons
 }
 
 // ---- many queries: one warp per query, K/V tiles shared by the CTA's 8 consecutive queries
-template <typename T, int NM>
+template <typename T, int NM, int MAXCV>
 __global__ void __launch_bounds__(QT * 32) window_attn_kernel(evo_window_attn_params p) {
   extern __shared__ float smem[];
   const int dk = p.dk, dv = p.dv, kw = NM * dk, kst = kw + 1;
@@ -133,7 +132,7 @@ __global__ void __launch_bounds__(QT * 32) window_attn_kernel(evo_window_attn_pa
   const int64_t win_lo = windowed ? max((int64_t)0, i_lo - p.window + 1) : 0;
   const int64_t keep_hi = windowed ? min(p.keep_first, win_lo) : 0;
 
-  Softmax<NM> sm;
+  Softmax<NM, MAXCV> sm;
   sm.init();
   for (int part = 0; part < 2; ++part) {
     const int64_t lo = part == 0 ? 0 : win_lo, hi = part == 0 ? keep_hi : i_hi + 1;       // keys [lo, hi)
@@ -153,7 +152,7 @@ __global__ void __launch_bounds__(QT * 32) window_attn_kernel(evo_window_attn_pa
       const int64_t kj = k0 + lane;
       const bool vis = lane < nk && kj <= i && (!windowed || i - kj < p.window || kj < p.keep_first);
       float pm[NM];
-      if (!tile_scores<NM>(sm, Qs + w * kw, Ks + (lane < nk ? lane : 0) * kst, dk, p.scale, vis, pm)) continue;
+      if (!tile_scores<NM, MAXCV>(sm, Qs + w * kw, Ks + (lane < nk ? lane : 0) * kst, dk, p.scale, vis, pm)) continue;
       for (int r = 0; r < nk; ++r) {
         float pr[NM];
 #pragma unroll
@@ -170,11 +169,11 @@ __global__ void __launch_bounds__(QT * 32) window_attn_kernel(evo_window_attn_pa
       }
     }
   }
-  if (valid) finish_row<T, NM>(p, sm, row, h, lane);
+  if (valid) finish_row<T, NM, MAXCV>(p, sm, row, h, lane);
 }
 
 // ---- few queries: one CTA per (query, head); its warps take the key tiles round-robin, straight from global memory
-template <typename T, int NM>
+template <typename T, int NM, int MAXCV>
 __global__ void __launch_bounds__(QT * 32) window_attn_split_kernel(evo_window_attn_params p) {
   extern __shared__ float smem[];
   const int dk = p.dk, dv = p.dv, kw = NM * dk;
@@ -195,7 +194,7 @@ __global__ void __launch_bounds__(QT * 32) window_attn_split_kernel(evo_window_a
   const int64_t keep_hi = windowed ? min(p.keep_first, win_lo) : 0;
   const int64_t n_keep = (keep_hi + KT - 1) / KT, n_win = (i + 1 - win_lo + KT - 1) / KT;
 
-  Softmax<NM> sm;
+  Softmax<NM, MAXCV> sm;
   sm.init();
   for (int64_t t = w; t < n_keep + n_win; t += QT) {
     const int64_t k0 = t < n_keep ? t * KT : win_lo + (t - n_keep) * KT;
@@ -246,7 +245,7 @@ __global__ void __launch_bounds__(QT * 32) window_attn_split_kernel(evo_window_a
   }
   __syncthreads();
   if (w != 0) return;
-  Softmax<NM> tot;
+  Softmax<NM, MAXCV> tot;
   tot.init();
 #pragma unroll
   for (int a = 0; a < NM; ++a) {
@@ -262,25 +261,32 @@ __global__ void __launch_bounds__(QT * 32) window_attn_split_kernel(evo_window_a
       for (int c = 0; c < MAXCV; ++c) tot.acc[a][c] = fmaf(src[2 + lane + 32 * c], sc, tot.acc[a][c]);
     }
   }
-  finish_row<T, NM>(p, tot, row, h, lane);
+  finish_row<T, NM, MAXCV>(p, tot, row, h, lane);
 }
 
-template <typename T, int NM>
-int launch(const evo_window_attn_params* p, cudaStream_t st) {
+template <typename T, int NM, int MAXCV>
+int launch_cv(const evo_window_attn_params* p, cudaStream_t st) {
   const int kw = NM * p->dk;
   if (p->Lq <= 4) {
     const size_t smem = sizeof(float) * ((size_t)kw + (size_t)QT * NM * (2 + MAXCV * 32));
-    auto kern = window_attn_split_kernel<T, NM>;
+    auto kern = window_attn_split_kernel<T, NM, MAXCV>;
     if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<dim3((unsigned)p->Lq, p->H, p->B), QT * 32, smem, st>>>(*p);
   } else {
     const size_t smem = sizeof(float) * ((size_t)KT * (kw + 1) + (size_t)KT * p->dv + (size_t)QT * kw);
     EVO_REQUIRE(smem <= 227 * 1024, "evo_window_attn_fwd: head too wide for shared memory (%zu bytes)", smem);
-    auto kern = window_attn_kernel<T, NM>;
+    auto kern = window_attn_kernel<T, NM, MAXCV>;
     if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<dim3((unsigned)((p->Lq + QT - 1) / QT), p->H, p->B), QT * 32, smem, st>>>(*p);
   }
   return check_launch("evo_window_attn_fwd");
+}
+
+template <typename T, int NM>
+int launch(const evo_window_attn_params* p, cudaStream_t st) {
+  if (p->dv <= 128) return launch_cv<T, NM, 4>(p, st);
+  if (p->dv <= 256) return launch_cv<T, NM, 8>(p, st);
+  return launch_cv<T, NM, 16>(p, st);
 }
 
 }  // namespace
@@ -289,7 +295,7 @@ extern "C" int evo_window_attn_fwd(const evo_window_attn_params* p, void* stream
   EVO_REQUIRE(p->q && p->k && p->v && p->out, "evo_window_attn_fwd: null argument");
   EVO_REQUIRE(p->B >= 0 && p->Lq >= 0 && p->H > 0 && p->G > 0 && p->H % p->G == 0 && p->dk > 0 && p->dv > 0, "evo_window_attn_fwd: bad shape");
   EVO_REQUIRE(p->n_maps == 1 || p->n_maps == 2, "evo_window_attn_fwd: n_maps must be 1 or 2");
-  EVO_REQUIRE(p->dv <= MAXCV * 32, "evo_window_attn_fwd: dv (%d) must be <= %d", p->dv, MAXCV * 32);
+  EVO_REQUIRE(p->dv <= 512, "evo_window_attn_fwd: dv (%d) must be <= 512", p->dv);
   EVO_REQUIRE(p->ldo >= (int64_t)p->H * p->dv, "evo_window_attn_fwd: ldo too small");
   if (p->B == 0 || p->Lq == 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;

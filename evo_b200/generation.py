@@ -65,6 +65,12 @@ class Generator:
             attn.seqlen_offset += 1
             rec.seqlen_offset += 1
 
+    def _vocab(self) -> int:
+        """Width of the model's logits (the tokenizer's vocabulary unless the model's configuration says otherwise)."""
+        cfg = getattr(self.model, "config", None)
+        v = cfg.get("vocab_size") if cfg is not None and hasattr(cfg, "get") else None
+        return int(v) if v else self.tokenizer.vocab_size
+
     def _pick(self, last_logits: torch.Tensor) -> torch.Tensor:
         return sample(last_logits, top_k=self.top_k, top_p=self.top_p, temperature=self.temperature)
 
@@ -79,7 +85,7 @@ class Generator:
         dev = window.device
         total = n_tail + num_tokens
         picked = torch.empty(n_seq, num_tokens, dtype=torch.long, device=dev)
-        kept_logits = torch.empty(n_seq, num_tokens, tk.vocab_size, dtype=torch.float, device=dev)
+        kept_logits = torch.empty(n_seq, num_tokens, self._vocab(), dtype=torch.float, device=dev)
         pick_args = dict(top_k=self.top_k, top_p=self.top_p, temperature=self.temperature)
         first = 0
         if resumed:
@@ -143,7 +149,7 @@ class Generator:
         n_tail = tail.shape[1]
 
         picked = torch.empty(n_seq, num_tokens, dtype=torch.long, device=dev)
-        kept_logits = torch.empty(n_seq, num_tokens, tk.vocab_size, dtype=torch.float, device=dev)
+        kept_logits = torch.empty(n_seq, num_tokens, self._vocab(), dtype=torch.float, device=dev)
         eos = torch.tensor([tk.eos], dtype=torch.long, device=device)
         state, cached_generation, resumed = self._state_for(n_seq, dev, cached_generation, inference_params_dict)
 

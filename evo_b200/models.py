@@ -150,5 +150,11 @@ class Evo:
         if model_name not in MODEL_NAMES:
             raise ValueError(f"Invalid model name {model_name}. Should be one of: {', '.join(MODEL_NAMES)}.")
         self.device = device
-        self.model = load_checkpoint(model_name=model_name, device=device, **load_kwargs)
+        model_dir = load_kwargs.get("model_dir")
+        if model_dir is not None and os.path.exists(os.path.join(model_dir, "config.json")):
+            # a checkpoint folder that names its own architecture (config.json): the registry picks the model class
+            load_kwargs = {k: v for k, v in load_kwargs.items() if k not in ("model_dir", "random_init")}
+            self.model = load_model_dir(model_dir, device=device, model_name=model_name, **load_kwargs)
+        else:
+            self.model = load_checkpoint(model_name=model_name, device=device, **load_kwargs)
         self.tokenizer = CharLevelTokenizer(512)

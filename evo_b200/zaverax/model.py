@@ -238,7 +238,9 @@ class Zaverax(KernelOps, nn.Module):
                          f_bias=w[f"l{i}.mix.f.b"].data_ptr(), lower=w[f"l{i}.mix.lower"].data_ptr(), norm_w=w[f"l{i}.mix.norm"].data_ptr(),
                          eps=self.config.eps, state=state.data_ptr() if state is not None else None, zero_start=zero,
                          out=out.data_ptr(), ldo=ldo, dtype=self._dt, B=B, L=L, H=m.heads, dk=m.dim, dv=m.vdim)
-        self._record("hgrn2", 3.0 * M * m.heads * m.dim * m.vdim, lambda: check(_lib.lib().evo_hgrn2_fwd(C.byref(hp), self._stream()), "evo_hgrn2_fwd"))
+        nws = _lib.lib().evo_hgrn2_workspace(C.byref(hp))
+        ws = torch.empty(nws, dtype=torch.uint8, device=dev) if nws else None
+        self._record("hgrn2", 3.0 * M * m.heads * m.dim * m.vdim, lambda: check(_lib.lib().evo_hgrn2_fwd(C.byref(hp), ptr(ws), nws, self._stream()), "evo_hgrn2_fwd"))
         return self._linear(out, pk["out"], M), pk["out"].Np
 
     def _attention(self, r, i, m, h, B, L, ip: Optional[InferenceParams], off: int, pos_dev):

@@ -332,7 +332,9 @@ typedef struct {
   void* out; int64_t ldo; int dtype;
   int B; int64_t L; int H, dk, dv;
 } evo_hgrn2_params;
-int evo_hgrn2_fwd(const evo_hgrn2_params* p, void* stream);
+/* workspace: evo_hgrn2_workspace() bytes (0 unless a head's state is too large for one CTA and is split by value channel) */
+size_t evo_hgrn2_workspace(const evo_hgrn2_params* p);
+int evo_hgrn2_fwd(const evo_hgrn2_params* p, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Softmax attention over a linear key/value cache with a sliding window that keeps the first tokens, n_maps (1 or 2) score
  * maps per head over the same values (differential attention: o = a1 - lambda * a2), an optional per-head RMS norm without
