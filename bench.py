@@ -1,6 +1,6 @@
 """bench.py — nucleotides/sec of the Evo-1 7B forward on B200 (BASELINE.json metric).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload 8k|131k|1k|32k|gen] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload 8k|131k|1k|32k|gen|zaverax] [--impl ours|reference]
 
 Workload "8k" (default, BASELINE.json configs[1]): evo-1-8k-base scoring forward, batch 8 x
 8192 nt of synthetic uniform ACGT (+BOS => L = 8193), bf16, random-init weights of the 7B
@@ -10,6 +10,8 @@ architecture (no network for checkpoints).  One "step" = one forward over one ba
           host strings -> pinned H2D -> forward -> fused log-softmax/gather -> D2H, per step.
 N > 1 (torchrun, one rank per GPU): independent replicas of the workload, no data-path
 collective (weak scaling); "131k" runs the sequence-parallel forward instead.
+Workload "zaverax" (an option; the default workload and its JSON contract are unchanged): the Zaverax design beside StripedHyena at
+equal layer sizes, prefill and decode, with a per-kernel roofline breakdown (bench_arch).
 --impl reference: the reference's own CPU implementation of the path.  stripedhyena==0.2.2 is
 not installable offline, so this arm times the oracle restatement (kind "port") on the host
 cores, rank 0 only, on a bounded sample of the same workload.
@@ -568,19 +570,139 @@ def bench_generate(args, wl):
         dist.destroy_process_group()
 
 
+ARCH_SIZES = {
+    # width, heads (of 128 channels), layers [recurrent, attention, recurrent, recurrent]; prefill batch x tokens; decode batch, context
+    "2k": dict(width=2048, heads=16, prefill=(4, 4096), decode=(16, 2048)),
+    "4k": dict(width=4096, heads=32, prefill=(4, 4096), decode=(16, 2048)),
+}
+
+
+def _arch_models(size, dev):
+    """A Zaverax model and a StripedHyena model of equal width, depth, head count and feed-forward width, random weights."""
+    import torch
+    from evo_b200.configs import get_config
+    from evo_b200.stripedhyena import StripedHyena, dotdict
+    from evo_b200.zaverax import Zaverax, ZaveraxConfig
+    s = ARCH_SIZES[size]
+    d, H = s["width"], s["heads"]
+    cfg = get_config("evo-1-8k-base")
+    cfg.update(hidden_size=d, num_filters=d, num_layers=4, num_attention_heads=H, attn_layer_idxs=[1], hyena_layer_idxs=[0, 2, 3])
+    torch.manual_seed(0)
+    with torch.device(dev):
+        sh = StripedHyena(dotdict(cfg))
+    sh.to_bfloat16_except_poles_residues()
+    ff = sh.blocks[0].mlp.inner
+    rec = {"type": "hgrn2", "mixer": {"heads": H, "dim": 128, "vdim": 128}, "mlp": {"kind": "dense", "ff": ff}}
+    att = {"type": "attention", "mixer": {"heads": H, "kv_heads": H, "dim": 64, "vdim": 128, "scale": 0.125, "diff": 0.5, "mask": {"size": 1024, "keep_first": 16}},
+           "mlp": {"kind": "dense", "ff": ff}}
+    zc = {"architecture": "Zaverax", "vocab": 512, "width": d, "layers": [rec, att, rec, rec], "norm": {"eps": 1e-5}, "canon": {"taps": 3},
+          "loop": {"start": 0, "stop": 0, "times": 1}, "residual_mult": 0.5, "logit_softcap": 15.0}
+    zv = Zaverax(ZaveraxConfig.from_dict(zc)).init_random(0, device=dev)
+    return zv, sh
+
+
+def bench_arch(args):
+    """--workload zaverax: prefill and decode throughput of the Zaverax design beside StripedHyena at equal layer sizes (random
+    weights, 4 layers each, one of them attention), with a per-kernel breakdown against the measured rooflines.  Inputs are larger
+    than L2 (16 Ki tokens x width); CUDA events; >= 3 warm-up steps."""
+    import torch
+    from evo_b200 import _lib
+    dev = "cuda:0"
+    peaks = measured_peaks()
+    steps = args.steps if args.steps is not None else 5
+    warmup = max(3, args.warmup if args.warmup is not None else 3)
+    fp32_lane_ops = 148 * 128 * peaks.get("sm_max_mhz", 1965.0) * 1e6        # CUDA-core fp32 instructions (lanes) per second at the maximum clock
+    bound = {"gemm": ("flop/s", peaks["bf16_tflops"] * 1e12), "gemm_simt": ("flop/s", 2 * fp32_lane_ops), "attn": ("flop/s", peaks["bf16_tflops"] * 1e12),
+             "window_attn": ("flop/s (CUDA cores)", 2 * fp32_lane_ops), "hgrn2": ("fp32 lane-op/s", fp32_lane_ops)}
+    out = {"workload": "zaverax", "metric": "tokens/sec, prefill and decode, Zaverax beside StripedHyena at equal sizes", "unit": "tok/s", "dtype": "bf16",
+           "data": "synthetic", "steps": steps, "warmup": warmup, "peaks": peaks, "sizes": {}}
+    launches = 0
+    with ClockSampler(0) as clocks:
+        for size, s in ARCH_SIZES.items():
+            zv, sh = _arch_models(size, dev)
+            rec = {}
+            for name, model in (("zaverax", zv), ("stripedhyena", sh)):
+                B, L = s["prefill"]
+                ids = torch.randint(0, 512, (B, L), device=dev)
+                fwd = lambda: model(ids)
+                for _ in range(warmup):
+                    fwd()
+                n0 = _lib.lib().evo_launch_count()
+                ms, _ = time_steps(fwd, steps, 1, dev)
+                launches += _lib.lib().evo_launch_count() - n0
+                by, _ = kernel_breakdown(model, fwd, 2, 1)
+                kinds = {}
+                for kind, (work, kms, n) in sorted(by.items()):
+                    unit, peak = bound.get(kind, ("B/s", peaks["hbm_gbs"] * 1e9))
+                    ach = work / (kms / 1e3) if kms > 0 else 0.0
+                    kinds[kind] = {"ms": kms, "launches": n, "achieved": ach, "unit": unit, "frac_of_measured_peak": ach / peak}
+                # decode: prompt through the stateful forward, then single-token steps
+                Bd, ctx = s["decode"]
+                pids = torch.randint(0, 512, (Bd, ctx), device=dev)
+                d = model.initialize_inference_params()
+                d["mha"].max_batch_size = d["hyena"].max_batch_size = Bd
+                d["mha"].max_seqlen = ctx + 512
+                lg, d = model(pids, inference_params_dict=d)
+                nsteps = 64
+                if name == "zaverax":
+                    tok0 = lg[:, -1].argmax(-1)
+                    model.decode_loop(tok0, d, 8, ctx, top_k=1)                       # warm-up: eager step + graph capture
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize()
+                    e0.record()
+                    model.decode_loop(tok0, d, nsteps, ctx + 8, top_k=1)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    dms = e0.elapsed_time(e1) / nsteps
+                else:
+                    d["mha"].seqlen_offset = d["hyena"].seqlen_offset = ctx
+                    nxt = lg[:, -1].argmax(-1, keepdim=True)
+                    def step():
+                        nonlocal nxt
+                        l2, _ = model(nxt, inference_params_dict=d)
+                        nxt = l2[:, -1].argmax(-1, keepdim=True)
+                        d["mha"].seqlen_offset += 1
+                        d["hyena"].seqlen_offset += 1
+                    for _ in range(4):
+                        step()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize()
+                    e0.record()
+                    for _ in range(nsteps):
+                        step()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    dms = e0.elapsed_time(e1) / nsteps
+                rec[name] = {"prefill_tok_s": B * L * steps / (ms / 1e3), "prefill_ms": ms / steps, "prefill_shape": [B, L], "kernels": kinds,
+                             "decode_tok_s": Bd / (dms / 1e3), "decode_ms_per_step": dms, "decode_shape": [Bd, ctx]}
+                del d, lg
+                torch.cuda.empty_cache()
+            out["sizes"][size] = rec
+            del zv, sh
+            torch.cuda.empty_cache()
+    out["value"] = out["sizes"]["4k"]["zaverax"]["prefill_tok_s"]
+    out["n_gpus"] = 1
+    out["gpu_launches"] = int(launches)
+    out["higher_is_better"] = True
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="8k", choices=list(WORKLOADS))
+    ap.add_argument("--workload", default="8k", choices=list(WORKLOADS) + ["zaverax"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sub", action="store_true", help="default workload only: skip the sp131k / gen sub-records")
     ap.add_argument("--no-gen", action="store_true", help="skip the cached-generation sub-record")
     ap.add_argument("--sub-steps", type=int, default=3, help="timed steps of the 131k sub-record")
     ap.add_argument("--gen-tokens", type=int, default=None, help="new tokens of the end-to-end generate() run (default: 4096 = BASELINE configs[3])")
     args = ap.parse_args()
+    if args.workload == "zaverax":
+        return bench_arch(args)
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":
         bench_reference(args, wl)

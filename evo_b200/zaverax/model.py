@@ -196,7 +196,9 @@ class Zaverax(KernelOps, nn.Module):
                             weight_offset=offset, eps=cfg.eps, out=out.data_ptr(), ldo=ldo, out_dtype=1 if out_f32 else self._dt,
                             B=B, seq_len=L, halo=halo, D=cfg.width, halo_src=halo_src.data_ptr() if halo_src is not None else None,
                             gather=gather.data_ptr() if gather is not None else None)
-        self._record("resid_norm", 8.0 * B * L * cfg.width, lambda: check(_lib.lib().evo_resid_norm(C.byref(p), self._stream()), "evo_resid_norm"))
+        esz = 4 if self._dt else 2
+        nbytes = B * L * cfg.width * (4.0 + (4.0 + esz if y is not None else 0.0) + (4.0 if x_add is not None else 0.0) + (4.0 if out_f32 else esz))
+        self._record("resid_norm", nbytes, lambda: check(_lib.lib().evo_resid_norm(C.byref(p), self._stream()), "evo_resid_norm"))
 
     def _mixer_input(self, r, i, x, y, ldy, B, L, rec: Optional[RecurrentInferenceParams], x_add):
         """x <- x + m*y (+ embedding output); h = norm1(x); returns h + conv(h) as (B*L, Kp) activations."""
@@ -215,7 +217,7 @@ class Zaverax(KernelOps, nn.Module):
             carry = rec.fir_state_dict[r] = torch.empty(B, halo, D, dtype=torch.float32, device=dev)
         cp = CausalConvParams(inp=hn.data_ptr(), weight=w[f"l{i}.canon1"].data_ptr(), out=h.data_ptr(), ldo=Kp, out_dtype=self._dt,
                               carry_out=carry.data_ptr() if carry is not None else None, B=B, seq_len=L, D=D, taps=cfg.taps)
-        self._record("causal_conv", 8.0 * B * L * D, lambda: check(_lib.lib().evo_causal_conv(C.byref(cp), self._stream()), "evo_causal_conv"))
+        self._record("causal_conv", B * L * D * (4.0 + h.element_size()), lambda: check(_lib.lib().evo_causal_conv(C.byref(cp), self._stream()), "evo_causal_conv"))
         return h
 
     def _hgrn2(self, r, i, m, h, B, L, rec: Optional[RecurrentInferenceParams]):
@@ -275,7 +277,7 @@ class Zaverax(KernelOps, nn.Module):
             ap.k_tok_stride = ap.v_tok_stride = cw
             ap.k_batch_stride = ap.v_batch_stride = cache.shape[1] * cw
         span = min(off + L, m.window + m.keep_first) if m.window > 0 else off + (L + 1) / 2.0
-        self._record("window_attn", 2.0 * M * m.heads * span * 2 * (m.dim + m.vdim), lambda: check(lib.evo_window_attn_fwd(C.byref(ap), self._stream()), "evo_window_attn_fwd"))
+        self._record("window_attn", 4.0 * M * m.heads * span * (m.dim + m.vdim), lambda: check(lib.evo_window_attn_fwd(C.byref(ap), self._stream()), "evo_window_attn_fwd"))
         return self._linear(out, pk["out"], M), pk["out"].Np
 
     def _feed_forward(self, i, layer, x, y, ldy, B, L):
@@ -286,7 +288,7 @@ class Zaverax(KernelOps, nn.Module):
         self._resid_norm(x, y, ldy, self.weights[f"l{i}.norm2"], 1.0, h, Kp, False, B, L)
         z = self._linear(h, pk["up"], M)
         a = torch.empty(M, pk["down"].Kp, dtype=self.act_dtype, device=dev)
-        self._record("polynorm", 4.0 * M * layer.ff, lambda: check(_lib.lib().evo_polynorm(
+        self._record("polynorm", 2.0 * z.element_size() * M * layer.ff, lambda: check(_lib.lib().evo_polynorm(
             ptr(z), pk["up"].Np, ptr(self.weights[f"l{i}.mlp.act"]), ptr(a), pk["down"].Kp, M, layer.ff, cfg.eps, self._dt, self._stream()), "evo_polynorm"))
         return self._linear(a, pk["down"], M), pk["down"].Np
 
