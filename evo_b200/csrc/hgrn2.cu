@@ -6,11 +6,15 @@
 // One CTA per (head, sequence).  A thread owns RPT consecutive state rows of one value channel: thread (kp, j) holds
 // S[kp*RPT .. kp*RPT+RPT) [j]; 16 tokens of activated gates / queries / values are staged in shared memory per round, so the
 // time loop runs without barriers; partial read-outs of the dk/RPT row groups are folded after each round.
+// Measured on B200: the time loop is bound by instruction issue and by the shared-memory -> register path of the (gate, query)
+// pairs, and it wants many resident warps: 1024 threads with 16 state rows each beat 512 threads x 32 rows, 256 threads x
+// (16 rows x 4 value channels) and a register-prefetched staging (3.1 vs 3.8, 4.7 and 6.3 ms per 4 x 4096 tokens x 32 heads of 128 x 128).
 // The same kernel serves the single-token step (L == 1): the state is then streamed through once.
 // Value channels are independent in the recurrence, so a head whose state does not fit one CTA's registers is split over
 // several CTAs by value channel; the read-outs then go to an fp32 workspace and a second small kernel applies the head norm.
 #include "common.cuh"
 #include "../../include/evo_b200.h"
+#include <algorithm>
 
 using namespace evo;
 
@@ -27,7 +31,7 @@ constexpr int TCH = 16;      // tokens staged per round
 
 template <typename T, int RPT>
 __global__ void __launch_bounds__(RPT <= 16 ? 1024 : (RPT == 32 ? 512 : 256)) hgrn2_kernel(evo_hgrn2_params p, int KP, int dvp, float* __restrict__ raw) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   const int dk = p.dk, dv = p.dv, dkp = KP * RPT;
   float2* fq = reinterpret_cast<float2*>(smem);            // [TCH][dkp]  (gate, activated query)
   float* vv = smem + 2 * TCH * dkp;                        // [TCH][dvp]
@@ -75,13 +79,15 @@ __global__ void __launch_bounds__(RPT <= 16 ? 1024 : (RPT == 32 ? 512 : 256)) hg
     __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
       const float v = vv[tt * dvp + (j - j0)];
-      const float2* e = fq + tt * dkp + kp * RPT;
+      const float4* e = reinterpret_cast<const float4*>(fq + tt * dkp + kp * RPT);       // two state rows per 16-byte read
       float o = 0.f;
 #pragma unroll
-      for (int r = 0; r < RPT; ++r) {
-        const float2 g = e[r];
-        S[r] = fmaf(g.x, S[r] - v, v);                 // g S + (1 - g) v
-        o = fmaf(S[r], g.y, o);
+      for (int r = 0; r < RPT / 2; ++r) {
+        const float4 g = e[r];
+        S[2 * r] = fmaf(g.x, S[2 * r] - v, v);         // g S + (1 - g) v
+        o = fmaf(S[2 * r], g.y, o);
+        S[2 * r + 1] = fmaf(g.z, S[2 * r + 1] - v, v);
+        o = fmaf(S[2 * r + 1], g.w, o);
       }
       op[(tt * KP + kp) * dvp + (j - j0)] = o;
     }
@@ -145,11 +151,18 @@ __global__ void head_norm_kernel(evo_hgrn2_params p, const float* __restrict__ r
 struct Plan { int rpt, KP, dvc, chunks; };
 // fewest state rows per thread that still fit one CTA (more threads hide the shared-memory latency of the time loop);
 // heads too large for that are split by value channel with 64 rows per thread
-inline Plan plan(int dk, int dv) {
+inline Plan plan(int dk, int dv, int64_t ctas, int64_t L) {
   const int dvp = (dv + 31) / 32 * 32;
   for (int rpt : {8, 16, 32, 64}) {
     const int KP = (dk + rpt - 1) / rpt;
-    if ((int64_t)KP * dvp <= (rpt <= 16 ? 1024 : (rpt == 32 ? 512 : 256))) return {rpt, KP, dvp, 1};      // register budget: rpt state rows per thread
+    if ((int64_t)KP * dvp <= (rpt <= 16 ? 1024 : (rpt == 32 ? 512 : 256))) {      // register budget: rpt state rows per thread
+      // long sequences on few (head, sequence) pairs: spread the value channels over more CTAs so that every SM has one
+      // (the extra fp32 round trip of the read-outs is small against a scan that leaves SMs idle)
+      int chunks = 1;
+      if (L >= 256 && ctas * 2 <= device_sm_count() && dvp >= 64) chunks = (int)std::min<int64_t>(dvp / 32, device_sm_count() / ctas);
+      const int dvc = (dvp / 32 + chunks - 1) / chunks * 32;
+      return {rpt, KP, dvc, (dv + dvc - 1) / dvc};
+    }
   }
   const int KP = (dk + 63) / 64;
   const int dvc = 256 / KP / 32 * 32;
@@ -172,7 +185,7 @@ int launch(const evo_hgrn2_params* p, int KP, int dvp, int chunks, float* raw, c
 
 template <typename T>
 int dispatch(const evo_hgrn2_params* p, void* workspace, size_t workspace_bytes, cudaStream_t st) {
-  const Plan pl = plan(p->dk, p->dv);
+  const Plan pl = plan(p->dk, p->dv, (int64_t)p->B * p->H, p->L);
   if (pl.rpt == 0) { set_error("evo_hgrn2_fwd: dk (%d) must be <= 512", p->dk); return -1; }
   float* raw = nullptr;
   if (pl.chunks > 1) {
@@ -189,7 +202,7 @@ int dispatch(const evo_hgrn2_params* p, void* workspace, size_t workspace_bytes,
 }  // namespace
 
 extern "C" size_t evo_hgrn2_workspace(const evo_hgrn2_params* p) {
-  const Plan pl = plan(p->dk, p->dv);
+  const Plan pl = plan(p->dk, p->dv, (int64_t)p->B * p->H, p->L);
   return pl.chunks > 1 ? sizeof(float) * (size_t)p->B * p->L * p->H * p->dv : 0;
 }
 

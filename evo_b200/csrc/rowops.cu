@@ -18,6 +18,16 @@ template <typename T> __device__ __forceinline__ void stf(T* p, float v);
 template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
+// 4 consecutive elements as floats (16-byte / 8-byte accesses; the callers check alignment and divisibility)
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const bf16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  return make_float4(bf_lo(u.x), bf_hi(u.x), bf_lo(u.y), bf_hi(u.y));
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(bf16* p, float4 v) { *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w)); }
+inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
 // sum over the block (blockDim.x <= 1024, a multiple of 32); every thread gets the total
 __device__ __forceinline__ float block_sum(float v, float* red) {
 #pragma unroll
@@ -45,7 +55,7 @@ __global__ void embed_f32_kernel(const IdT* __restrict__ ids, const bf16* __rest
 // ------------------------------------------------------------------ residual update + RMS norm
 // One CTA per output row.  Output rows are laid out (B, halo + L, .): rows t < halo of a sequence are copies of carried
 // rows (or zeros); the others are norm(x_row) with x_row <- x_row + y_scale * y_row + add_row written back first.
-template <typename TY, typename TO>
+template <typename TY, typename TO, bool VEC>
 __global__ void __launch_bounds__(256) resid_norm_kernel(evo_resid_norm_params p) {
   __shared__ float red[32];
   const int64_t per = p.halo + p.seq_len;
@@ -64,6 +74,32 @@ __global__ void __launch_bounds__(256) resid_norm_kernel(evo_resid_norm_params p
   const float* ar = p.x_add ? p.x_add + srow * D : nullptr;
   const bool update = (yr != nullptr || ar != nullptr) && p.gather == nullptr;
   float ss = 0.f;
+  if (VEC) {                              // D, ldy, ldo multiples of 4 and 16-byte aligned rows: 4 channels per access
+    for (int c = threadIdx.x * 4; c < D; c += blockDim.x * 4) {
+      float4 v = ld4(xr + c);
+      if (yr) { const float4 y4 = ld4(yr + c); v.x = fmaf(p.y_scale, y4.x, v.x); v.y = fmaf(p.y_scale, y4.y, v.y); v.z = fmaf(p.y_scale, y4.z, v.z); v.w = fmaf(p.y_scale, y4.w, v.w); }
+      if (ar) { const float4 a4 = ld4(ar + c); v.x += a4.x; v.y += a4.y; v.z += a4.z; v.w += a4.w; }
+      if (update) st4(xr + c, v);
+      ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+    }
+    ss = block_sum(ss, red);
+    const float rstd = 1.0f / sqrtf(ss / (float)D + p.eps);
+    const bf16* w = (const bf16*)p.weight;
+    for (int c = threadIdx.x * 4; c < p.ldo; c += blockDim.x * 4) {
+      float4 h = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (c < D) {
+        float4 v = ld4(xr + c);
+        if (!update) {
+          if (yr) { const float4 y4 = ld4(yr + c); v.x = fmaf(p.y_scale, y4.x, v.x); v.y = fmaf(p.y_scale, y4.y, v.y); v.z = fmaf(p.y_scale, y4.z, v.z); v.w = fmaf(p.y_scale, y4.w, v.w); }
+          if (ar) { const float4 a4 = ld4(ar + c); v.x += a4.x; v.y += a4.y; v.z += a4.z; v.w += a4.w; }
+        }
+        h = make_float4(v.x * rstd, v.y * rstd, v.z * rstd, v.w * rstd);
+        if (w) { const float4 w4 = ld4(w + c); h.x *= p.weight_offset + w4.x; h.y *= p.weight_offset + w4.y; h.z *= p.weight_offset + w4.z; h.w *= p.weight_offset + w4.w; }
+      }
+      st4(orow + c, h);
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < D; c += blockDim.x) {
     float v = xr[c];
     if (yr) v = fmaf(p.y_scale, ldf(yr + c), v);
@@ -92,7 +128,7 @@ __global__ void __launch_bounds__(256) resid_norm_kernel(evo_resid_norm_params p
 // ------------------------------------------------------------------ per-channel causal convolution with a skip path
 // in (B, taps-1 + L, D) fp32: the first taps-1 rows of a sequence are the carried inputs.  out[b,t,c] = in[b,taps-1+t,c] +
 // sum_j w[c,j] * in[b,t+j,c]; the last taps-1 input rows become the next carried rows.
-template <typename TO>
+template <typename TO, bool VEC>
 __global__ void __launch_bounds__(256) causal_conv_kernel(evo_causal_conv_params p) {
   const int halo = p.taps - 1;
   const int64_t per = p.seq_len + halo;
@@ -107,6 +143,24 @@ __global__ void __launch_bounds__(256) causal_conv_kernel(evo_causal_conv_params
     return;
   }
   TO* orow = (TO*)p.out + (b * p.seq_len + t) * p.ldo;
+  if (VEC) {                              // D and ldo multiples of 4, 16-byte aligned rows: 4 channels per access
+    for (int c = threadIdx.x * 4; c < p.ldo; c += blockDim.x * 4) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (c < p.D) {
+        acc = ld4(in + (t + halo) * (int64_t)p.D + c);
+        for (int j = 0; j < p.taps; ++j) {
+          const float4 v = ld4(in + (t + j) * (int64_t)p.D + c);
+          const bf16* wc = w + (int64_t)c * p.taps + j;
+          acc.x = fmaf(__bfloat162float(wc[0]), v.x, acc.x);
+          acc.y = fmaf(__bfloat162float(wc[p.taps]), v.y, acc.y);
+          acc.z = fmaf(__bfloat162float(wc[2 * p.taps]), v.z, acc.z);
+          acc.w = fmaf(__bfloat162float(wc[3 * p.taps]), v.w, acc.w);
+        }
+      }
+      st4(orow + c, acc);
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < p.ldo; c += blockDim.x) {
     float acc = 0.f;
     if (c < p.D) {
@@ -119,22 +173,45 @@ __global__ void __launch_bounds__(256) causal_conv_kernel(evo_causal_conv_params
 
 // ------------------------------------------------------------------ PolyNorm: a N(z) + b N(z^2) + c N(z^3) + e
 // N divides a row by its root mean square; one CTA per row, two passes over the row (the second one hits L1/L2).
-template <typename T>
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) polynorm_kernel(const T* __restrict__ z, int64_t ldz, const bf16* __restrict__ coef, T* __restrict__ out,
                                                        int64_t ldo, int F, float eps) {
   __shared__ float red[32];
   const T* zr = z + (int64_t)blockIdx.x * ldz;
   T* orow = out + (int64_t)blockIdx.x * ldo;
   float s1 = 0.f, s2 = 0.f, s3 = 0.f;
-  for (int c = threadIdx.x; c < F; c += blockDim.x) {
-    const float v = ldf(zr + c), v2 = v * v, v3 = v2 * v;
-    s1 = fmaf(v, v, s1); s2 = fmaf(v2, v2, s2); s3 = fmaf(v3, v3, s3);
+  if (VEC) {
+    for (int c = threadIdx.x * 4; c < F; c += blockDim.x * 4) {
+      const float4 q = ld4(zr + c);
+      const float e[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { const float v = e[i], v2 = v * v, v3 = v2 * v; s1 = fmaf(v, v, s1); s2 = fmaf(v2, v2, s2); s3 = fmaf(v3, v3, s3); }
+    }
+  } else {
+    for (int c = threadIdx.x; c < F; c += blockDim.x) {
+      const float v = ldf(zr + c), v2 = v * v, v3 = v2 * v;
+      s1 = fmaf(v, v, s1); s2 = fmaf(v2, v2, s2); s3 = fmaf(v3, v3, s3);
+    }
   }
   s1 = block_sum(s1, red); s2 = block_sum(s2, red); s3 = block_sum(s3, red);
   const float a = __bfloat162float(coef[0]) / sqrtf(s1 / (float)F + eps);
   const float b = __bfloat162float(coef[1]) / sqrtf(s2 / (float)F + eps);
   const float c3 = __bfloat162float(coef[2]) / sqrtf(s3 / (float)F + eps);
   const float e = __bfloat162float(coef[3]);
+  if (VEC) {
+    for (int c = threadIdx.x * 4; c < ldo; c += blockDim.x * 4) {
+      float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (c < F) {
+        const float4 q = ld4(zr + c);
+        o.x = fmaf(a, q.x, fmaf(b, q.x * q.x, fmaf(c3, q.x * q.x * q.x, e)));
+        o.y = fmaf(a, q.y, fmaf(b, q.y * q.y, fmaf(c3, q.y * q.y * q.y, e)));
+        o.z = fmaf(a, q.z, fmaf(b, q.z * q.z, fmaf(c3, q.z * q.z * q.z, e)));
+        o.w = fmaf(a, q.w, fmaf(b, q.w * q.w, fmaf(c3, q.w * q.w * q.w, e)));
+      }
+      st4(orow + c, o);
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < ldo; c += blockDim.x) {
     float o = 0.f;
     if (c < F) {
@@ -183,12 +260,18 @@ extern "C" int evo_resid_norm(const evo_resid_norm_params* p, void* stream) {
   if (rows == 0 || p->seq_len == 0) return 0;
   dim3 grid((unsigned)rows), block(p->D >= 1024 ? 256 : 128);
   cudaStream_t st = (cudaStream_t)stream;
-  const int key = (p->y_dtype ? 2 : 0) | (p->out_dtype ? 1 : 0);
+  const bool vec = p->D % 4 == 0 && p->ldo % 4 == 0 && (p->y == nullptr || p->ldy % 4 == 0) && aligned16(p->x) && aligned16(p->out) && aligned16(p->y) &&
+                   aligned16(p->x_add) && aligned16(p->weight) && aligned16(p->halo_src);
+  const int key = (p->y_dtype ? 4 : 0) | (p->out_dtype ? 2 : 0) | (vec ? 1 : 0);
   switch (key) {
-    case 0: resid_norm_kernel<bf16, bf16><<<grid, block, 0, st>>>(*p); break;
-    case 1: resid_norm_kernel<bf16, float><<<grid, block, 0, st>>>(*p); break;
-    case 2: resid_norm_kernel<float, bf16><<<grid, block, 0, st>>>(*p); break;
-    default: resid_norm_kernel<float, float><<<grid, block, 0, st>>>(*p); break;
+    case 0: resid_norm_kernel<bf16, bf16, false><<<grid, block, 0, st>>>(*p); break;
+    case 1: resid_norm_kernel<bf16, bf16, true><<<grid, block, 0, st>>>(*p); break;
+    case 2: resid_norm_kernel<bf16, float, false><<<grid, block, 0, st>>>(*p); break;
+    case 3: resid_norm_kernel<bf16, float, true><<<grid, block, 0, st>>>(*p); break;
+    case 4: resid_norm_kernel<float, bf16, false><<<grid, block, 0, st>>>(*p); break;
+    case 5: resid_norm_kernel<float, bf16, true><<<grid, block, 0, st>>>(*p); break;
+    case 6: resid_norm_kernel<float, float, false><<<grid, block, 0, st>>>(*p); break;
+    default: resid_norm_kernel<float, float, true><<<grid, block, 0, st>>>(*p); break;
   }
   return check_launch("evo_resid_norm");
 }
@@ -198,8 +281,10 @@ extern "C" int evo_causal_conv(const evo_causal_conv_params* p, void* stream) {
   const int64_t rows = (int64_t)p->B * (p->seq_len + p->taps - 1);
   if (rows == 0) return 0;
   dim3 grid((unsigned)rows), block(p->D >= 1024 ? 256 : 128);
-  if (p->out_dtype) causal_conv_kernel<float><<<grid, block, 0, (cudaStream_t)stream>>>(*p);
-  else causal_conv_kernel<bf16><<<grid, block, 0, (cudaStream_t)stream>>>(*p);
+  const bool vec = p->D % 4 == 0 && p->ldo % 4 == 0 && aligned16(p->in) && aligned16(p->out);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (p->out_dtype) { if (vec) causal_conv_kernel<float, true><<<grid, block, 0, st>>>(*p); else causal_conv_kernel<float, false><<<grid, block, 0, st>>>(*p); }
+  else { if (vec) causal_conv_kernel<bf16, true><<<grid, block, 0, st>>>(*p); else causal_conv_kernel<bf16, false><<<grid, block, 0, st>>>(*p); }
   return check_launch("evo_causal_conv");
 }
 
@@ -207,8 +292,15 @@ extern "C" int evo_polynorm(const void* z, int64_t ldz, const void* coef, void* 
   EVO_REQUIRE(z && out && coef && F > 0 && ldz >= F && ldo >= F, "evo_polynorm: bad arguments");
   if (rows == 0) return 0;
   dim3 grid((unsigned)rows), block(256);
-  if (dtype) polynorm_kernel<float><<<grid, block, 0, (cudaStream_t)stream>>>((const float*)z, ldz, (const bf16*)coef, (float*)out, ldo, F, eps);
-  else polynorm_kernel<bf16><<<grid, block, 0, (cudaStream_t)stream>>>((const bf16*)z, ldz, (const bf16*)coef, (bf16*)out, ldo, F, eps);
+  const bool vec = F % 4 == 0 && ldz % 4 == 0 && ldo % 4 == 0 && aligned16(z) && aligned16(out);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype) {
+    if (vec) polynorm_kernel<float, true><<<grid, block, 0, st>>>((const float*)z, ldz, (const bf16*)coef, (float*)out, ldo, F, eps);
+    else polynorm_kernel<float, false><<<grid, block, 0, st>>>((const float*)z, ldz, (const bf16*)coef, (float*)out, ldo, F, eps);
+  } else {
+    if (vec) polynorm_kernel<bf16, true><<<grid, block, 0, st>>>((const bf16*)z, ldz, (const bf16*)coef, (bf16*)out, ldo, F, eps);
+    else polynorm_kernel<bf16, false><<<grid, block, 0, st>>>((const bf16*)z, ldz, (const bf16*)coef, (bf16*)out, ldo, F, eps);
+  }
   return check_launch("evo_polynorm");
 }
 
