@@ -12,8 +12,13 @@
 #include "common.cuh"
 #include "../../include/evo_b200.h"
 #include <math.h>
+#include <stdlib.h>
 
 using namespace evo;
+
+namespace evo {
+int window_attn_mma(const evo_window_attn_params* p, cudaStream_t st);      // window_attention_mma.cu; 1 = shape not covered
+}
 
 namespace {
 
@@ -299,6 +304,11 @@ extern "C" int evo_window_attn_fwd(const evo_window_attn_params* p, void* stream
   EVO_REQUIRE(p->ldo >= (int64_t)p->H * p->dv, "evo_window_attn_fwd: ldo too small");
   if (p->B == 0 || p->Lq == 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
+  static const char* env_mma = getenv("EVO_B200_WINDOW_ATTN_MMA");      // "0": always the CUDA-core kernel (comparisons)
+  if (!(env_mma && atoi(env_mma) == 0)) {
+    const int rc = window_attn_mma(p, st);                              // bf16, two maps, >= 16 query rows, heads up to 128
+    if (rc <= 0) return rc;
+  }
   if (p->dtype) return p->n_maps == 2 ? launch<float, 2>(p, st) : launch<float, 1>(p, st);
   return p->n_maps == 2 ? launch<bf16, 2>(p, st) : launch<bf16, 1>(p, st);
 }

@@ -1,0 +1,285 @@
+// Tensor-core form of the windowed multi-map attention (see window_attention.cu for the mechanism) for bf16 activations.
+// The fp32 rule of the design is kept: scores are exact bf16 x bf16 products accumulated in fp32 (mma.sync m16n8k16), the softmax
+// runs in fp32 registers, and each probability enters P.V as a bf16 high part plus a bf16 low part (two MMAs, relative error
+// 2^-17 per weight instead of 2^-9), accumulated in fp32.
+//
+// CTA = 4 warps x 16 queries, 64-key tiles of K (both maps) and V in shared memory as bf16, row-major with 16-byte row padding
+// (conflict-free fragment reads; V fragments come transposed out of ldmatrix), filled with 16-byte copies when the head sizes and
+// strides are multiples of 8.  A warp keeps both maps' output accumulators (16 x dv fp32 each) in registers and handles one map
+// at a time (scores -> softmax -> P.V), so only one 16 x 64 tile of probabilities is live.
+// Head sizes are padded to 16 in shared memory (zero columns); dk <= 128, dv <= 128 and dv % 8 == 0, otherwise the CUDA-core
+// kernel runs.  The tile walk is the CUDA-core kernel's: [0, keep_first) and the union of the CTA's windows.
+#include "common.cuh"
+#include "../../include/evo_b200.h"
+#include <math.h>
+
+using namespace evo;
+
+namespace evo {
+int window_attn_mma(const evo_window_attn_params* p, cudaStream_t st);      // returns 1 when the shape is not covered
+}
+
+namespace {
+
+constexpr int WARPS = 4, QROWS = 16, KT = 64;
+
+__device__ __forceinline__ void mma_bf16(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, const void* smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem_row)));
+}
+__device__ __forceinline__ float quad_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float quad_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+// bf16 high part and bf16 residual of two probabilities
+__device__ __forceinline__ void split_pack(float x, float y, uint32_t& hi, uint32_t& lo) {
+  const bf16 xh = __float2bfloat16_rn(x), yh = __float2bfloat16_rn(y);
+  hi = (uint32_t)__bfloat16_as_ushort(xh) | ((uint32_t)__bfloat16_as_ushort(yh) << 16);
+  lo = pack_bf16(x - __bfloat162float(xh), y - __bfloat162float(yh));
+}
+
+// NV8 = padded dv / 8 (output tiles of 8 channels per warp row block)
+template <int NV8>
+__global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_attn_params p, int dkp, int qst, int kst, int vst, int vec) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [WARPS*16][qst]   both maps' queries
+  bf16* Ks = Qs + WARPS * QROWS * qst;                           // [KT][kst]         both maps' keys
+  bf16* Vs = Ks + KT * kst;                                      // [KT][vst]         values
+  const int dk = p.dk, dv = p.dv;
+  const int b = blockIdx.z, h = blockIdx.y, g = h / (p.H / p.G);
+  const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, qr = lane >> 2, qc = (lane & 3) * 2;
+  const int64_t pos = p.pos_dev ? (int64_t)*p.pos_dev : p.q_pos0;
+  const int64_t rel0 = (int64_t)blockIdx.x * (WARPS * QROWS);
+  const bf16* qg = (const bf16*)p.q;
+  // queries of the CTA: [row][map][dkp], zero padding for rows past Lq and columns past dk
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  if (vec) {                              // dk, dv, strides multiples of 8 and 16-byte aligned bases: 8 elements per copy
+    const int c8n = 2 * dkp / 8;
+    for (int idx = tid; idx < WARPS * QROWS * c8n; idx += WARPS * 32) {
+      const int r = idx / c8n, c = (idx % c8n) * 8, m = c / dkp, e = c % dkp;
+      const int64_t rel = rel0 + r;
+      uint4 v = zero4;
+      if (rel < p.Lq && e < dk) v = *reinterpret_cast<const uint4*>(qg + ((int64_t)b * p.Lq + rel) * p.q_tok_stride + (int64_t)h * 2 * dk + m * dk + e);
+      *reinterpret_cast<uint4*>(Qs + r * qst + c) = v;
+    }
+  } else {
+    for (int idx = tid; idx < WARPS * QROWS * 2 * dkp; idx += WARPS * 32) {
+      const int r = idx / (2 * dkp), c = idx % (2 * dkp), m = c / dkp, e = c % dkp;
+      const int64_t rel = rel0 + r;
+      bf16 v = __float2bfloat16_rn(0.f);
+      if (rel < p.Lq && e < dk) v = qg[((int64_t)b * p.Lq + rel) * p.q_tok_stride + (int64_t)h * 2 * dk + m * dk + e];
+      Qs[r * qst + c] = v;
+    }
+  }
+  const bf16* kb = (const bf16*)p.k + (int64_t)b * p.k_batch_stride + (int64_t)g * 2 * dk;
+  const bf16* vb = (const bf16*)p.v + (int64_t)b * p.v_batch_stride + (int64_t)g * dv;
+  const int64_t i_lo = pos + rel0, i_hi = pos + min(p.Lq - 1, rel0 + WARPS * QROWS - 1);
+  const bool windowed = p.window > 0;
+  const int64_t win_lo = windowed ? max((int64_t)0, i_lo - p.window + 1) : 0;
+  const int64_t keep_hi = windowed ? min(p.keep_first, win_lo) : 0;
+  // this warp's rows
+  const int64_t i0 = pos + rel0 + w * QROWS + qr, i1 = i0 + 8;                // positions of the thread's two rows
+  const int64_t wi_lo = pos + rel0 + w * QROWS, wi_hi = wi_lo + QROWS - 1;     // the warp's first / last position
+
+  float O[2][NV8][4];
+  float mrun[2][2], lrun[2][2];
+#pragma unroll
+  for (int m = 0; m < 2; ++m) {
+    mrun[m][0] = mrun[m][1] = -INFINITY; lrun[m][0] = lrun[m][1] = 0.f;
+#pragma unroll
+    for (int n = 0; n < NV8; ++n) O[m][n][0] = O[m][n][1] = O[m][n][2] = O[m][n][3] = 0.f;
+  }
+  const bf16* Qw = Qs + (w * QROWS) * qst;
+  const float scale2 = p.scale * 1.4426950408889634f;
+
+  for (int part = 0; part < 2; ++part) {
+    const int64_t lo = part == 0 ? 0 : win_lo, hi = part == 0 ? keep_hi : i_hi + 1;
+    for (int64_t k0 = lo; k0 < hi; k0 += KT) {
+      const int nk = (int)min((int64_t)KT, hi - k0);
+      __syncthreads();
+      if (vec) {
+        const int c8n = 2 * dkp / 8;
+        for (int idx = tid; idx < KT * c8n; idx += WARPS * 32) {
+          const int r = idx / c8n, c = (idx % c8n) * 8, m = c / dkp, e = c % dkp;
+          uint4 v = zero4;
+          if (r < nk && e < dk) v = *reinterpret_cast<const uint4*>(kb + (k0 + r) * p.k_tok_stride + m * dk + e);
+          *reinterpret_cast<uint4*>(Ks + r * kst + c) = v;
+        }
+        for (int idx = tid; idx < KT * NV8; idx += WARPS * 32) {
+          const int r = idx / NV8, c = (idx % NV8) * 8;
+          uint4 v = zero4;
+          if (r < nk && c < dv) v = *reinterpret_cast<const uint4*>(vb + (k0 + r) * p.v_tok_stride + c);
+          *reinterpret_cast<uint4*>(Vs + r * vst + c) = v;
+        }
+      } else {
+        for (int idx = tid; idx < KT * 2 * dkp; idx += WARPS * 32) {
+          const int r = idx / (2 * dkp), c = idx % (2 * dkp), m = c / dkp, e = c % dkp;
+          bf16 v = __float2bfloat16_rn(0.f);
+          if (r < nk && e < dk) v = kb[(k0 + r) * p.k_tok_stride + m * dk + e];
+          Ks[r * kst + c] = v;
+        }
+        for (int idx = tid; idx < KT * NV8 * 8; idx += WARPS * 32) {
+          const int r = idx / (NV8 * 8), c = idx % (NV8 * 8);
+          bf16 v = __float2bfloat16_rn(0.f);
+          if (r < nk && c < dv) v = vb[(k0 + r) * p.v_tok_stride + c];
+          Vs[r * vst + c] = v;
+        }
+      }
+      __syncthreads();
+      // a tile none of the warp's rows can see
+      const int64_t t_lo = k0, t_hi = k0 + nk - 1;
+      if (t_lo > wi_hi) continue;
+      if (windowed && wi_lo - t_hi >= p.window && t_lo >= p.keep_first) continue;
+
+#pragma unroll
+      for (int m = 0; m < 2; ++m) {
+        // scores of map m: S (16 x 64) = Q_m (16 x dkp) . K_m^T
+        float Pm[1][KT / 8][4];
+#pragma unroll
+        for (int n = 0; n < KT / 8; ++n) Pm[0][n][0] = Pm[0][n][1] = Pm[0][n][2] = Pm[0][n][3] = 0.f;
+        for (int ks = 0; ks < dkp / 16; ++ks) {
+          uint32_t a[4];
+          const bf16* qa = Qw + m * dkp + ks * 16 + qc;
+          a[0] = *reinterpret_cast<const uint32_t*>(qa + qr * qst);
+          a[1] = *reinterpret_cast<const uint32_t*>(qa + (qr + 8) * qst);
+          a[2] = *reinterpret_cast<const uint32_t*>(qa + qr * qst + 8);
+          a[3] = *reinterpret_cast<const uint32_t*>(qa + (qr + 8) * qst + 8);
+#pragma unroll
+          for (int n = 0; n < KT / 8; ++n) {
+            const bf16* kbp = Ks + (n * 8 + qr) * kst + m * dkp + ks * 16 + qc;
+            mma_bf16(Pm[0][n], a, *reinterpret_cast<const uint32_t*>(kbp), *reinterpret_cast<const uint32_t*>(kbp + 8));
+          }
+        }
+        // mask, running max / sum, probabilities
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < KT / 8; ++n) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int64_t kj = k0 + n * 8 + qc + (c & 1);
+            const int64_t i = (c < 2) ? i0 : i1;
+            const bool vis = (n * 8 + qc + (c & 1)) < nk && kj <= i && (!windowed || i - kj < p.window || kj < p.keep_first);
+            const float s = vis ? Pm[0][n][c] * scale2 : -INFINITY;        // base-2 exponent: exp(x) = 2^(x log2 e)
+            Pm[0][n][c] = s;
+            if (c < 2) mx0 = fmaxf(mx0, s); else mx1 = fmaxf(mx1, s);
+          }
+        }
+        mx0 = quad_max(mx0); mx1 = quad_max(mx1);
+        const float mn0 = fmaxf(mrun[m][0], mx0), mn1 = fmaxf(mrun[m][1], mx1);
+        // rows that have seen no key yet keep max = -inf: use 0 as the reference so that exp() gives 0, not NaN
+        const float r0 = mn0 == -INFINITY ? 0.f : mn0, r1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float c0 = exp2f(mrun[m][0] - r0), c1 = exp2f(mrun[m][1] - r1);
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int n = 0; n < KT / 8; ++n) {
+          Pm[0][n][0] = exp2f(Pm[0][n][0] - r0); Pm[0][n][1] = exp2f(Pm[0][n][1] - r0);
+          Pm[0][n][2] = exp2f(Pm[0][n][2] - r1); Pm[0][n][3] = exp2f(Pm[0][n][3] - r1);
+          s0 += Pm[0][n][0] + Pm[0][n][1]; s1 += Pm[0][n][2] + Pm[0][n][3];
+        }
+        lrun[m][0] = lrun[m][0] * c0 + quad_sum(s0); lrun[m][1] = lrun[m][1] * c1 + quad_sum(s1);
+        mrun[m][0] = mn0; mrun[m][1] = mn1;
+#pragma unroll
+        for (int n = 0; n < NV8; ++n) { O[m][n][0] *= c0; O[m][n][1] *= c0; O[m][n][2] *= c1; O[m][n][3] *= c1; }
+        // O_m += P_m . V: high and low bf16 parts of P against the same V fragments (ldmatrix, transposed on the way)
+#pragma unroll
+        for (int kk = 0; kk < KT / 16; ++kk) {
+          uint32_t ah[4], al[4];
+          split_pack(Pm[0][2 * kk][0], Pm[0][2 * kk][1], ah[0], al[0]);
+          split_pack(Pm[0][2 * kk][2], Pm[0][2 * kk][3], ah[1], al[1]);
+          split_pack(Pm[0][2 * kk + 1][0], Pm[0][2 * kk + 1][1], ah[2], al[2]);
+          split_pack(Pm[0][2 * kk + 1][2], Pm[0][2 * kk + 1][3], ah[3], al[3]);
+#pragma unroll
+          for (int n = 0; n < NV8; n += 2) {
+            uint32_t bv[4];          // b0, b1 of channel tile n, then of tile n + 1
+            ldmatrix_x4_trans(bv, Vs + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * vst + (n + (lane >> 4)) * 8);
+            mma_bf16(O[m][n], ah, bv[0], bv[1]); mma_bf16(O[m][n], al, bv[0], bv[1]);
+            mma_bf16(O[m][n + 1], ah, bv[2], bv[3]); mma_bf16(O[m][n + 1], al, bv[2], bv[3]);
+          }
+        }
+      }
+    }
+  }
+  // o = a1 / l1 - lambda * a2 / l2, head norm, gate, store
+  const int64_t rel_a = rel0 + w * QROWS + qr, rel_b = rel_a + 8;
+  const float il[2][2] = {{1.f / lrun[0][0], 1.f / lrun[0][1]}, {1.f / lrun[1][0], 1.f / lrun[1][1]}};
+  float ss0 = 0.f, ss1 = 0.f;
+#pragma unroll
+  for (int n = 0; n < NV8; ++n) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int r = c >> 1;
+      const float v = O[0][n][c] * il[0][r] - p.lambda * (O[1][n][c] * il[1][r]);
+      const bool live = n * 8 + qc + (c & 1) < dv;
+      O[0][n][c] = live ? v : 0.f;
+      if (r == 0) ss0 = fmaf(O[0][n][c], O[0][n][c], ss0); else ss1 = fmaf(O[0][n][c], O[0][n][c], ss1);
+    }
+  }
+  float mul0 = 1.f, mul1 = 1.f;
+  if (p.head_norm) {
+    mul0 = p.out_scale / sqrtf(quad_sum(ss0) / (float)dv + p.norm_eps);
+    mul1 = p.out_scale / sqrtf(quad_sum(ss1) / (float)dv + p.norm_eps);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int64_t rel = r == 0 ? rel_a : rel_b;
+    if (rel >= p.Lq) continue;
+    const int64_t row = (int64_t)b * p.Lq + rel;
+    bf16* orow = (bf16*)p.out + row * p.ldo + (int64_t)h * dv;
+    const bf16* grow = p.gate ? (const bf16*)p.gate + row * p.gate_tok_stride + (int64_t)h * dv : nullptr;
+    const float mul = r == 0 ? mul0 : mul1;
+#pragma unroll
+    for (int n = 0; n < NV8; ++n) {
+      const int ch = n * 8 + qc;
+      if (ch < dv) {                                   // dv is even: the pair (ch, ch + 1) is inside the head
+        float v0 = O[0][n][2 * r] * mul, v1 = O[0][n][2 * r + 1] * mul;
+        if (grow) {
+          v0 *= 1.f / (1.f + expf(-__bfloat162float(grow[ch])));
+          v1 *= 1.f / (1.f + expf(-__bfloat162float(grow[ch + 1])));
+        }
+        orow[ch] = __float2bfloat16_rn(v0);
+        orow[ch + 1] = __float2bfloat16_rn(v1);
+      }
+    }
+    if (h == p.H - 1)
+      for (int64_t c = (int64_t)p.H * dv + (lane & 3); c < p.ldo; c += 4) ((bf16*)p.out)[row * p.ldo + c] = __float2bfloat16_rn(0.f);
+  }
+}
+
+template <int NV8>
+int launch(const evo_window_attn_params* p, cudaStream_t st) {
+  const int dkp = (p->dk + 15) / 16 * 16;
+  const int qst = 2 * dkp + 8, kst = 2 * dkp + 8, vst = NV8 * 8 + 8;
+  const size_t smem = sizeof(bf16) * ((size_t)WARPS * QROWS * qst + (size_t)KT * kst + (size_t)KT * vst);
+  auto a16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
+  const int vec = p->dk % 8 == 0 && p->dv % 8 == 0 && p->q_tok_stride % 8 == 0 && p->k_tok_stride % 8 == 0 && p->v_tok_stride % 8 == 0 &&
+                  p->k_batch_stride % 8 == 0 && p->v_batch_stride % 8 == 0 && a16(p->q) && a16(p->k) && a16(p->v);
+  auto kern = window_attn_mma_kernel<NV8>;
+  if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<dim3((unsigned)((p->Lq + WARPS * QROWS - 1) / (WARPS * QROWS)), p->H, p->B), WARPS * 32, smem, st>>>(*p, dkp, qst, kst, vst, vec);
+  return check_launch("evo_window_attn_fwd");
+}
+
+}  // namespace
+
+int evo::window_attn_mma(const evo_window_attn_params* p, cudaStream_t st) {
+  if (p->dtype != 0 || p->n_maps != 2 || p->dk > 128 || p->dv > 128 || p->dv % 8 != 0 || p->Lq < 16) return 1;
+  const int nv8 = (p->dv + 15) / 16 * 2;
+  switch (nv8) {
+    case 2: return launch<2>(p, st);
+    case 4: return launch<4>(p, st);
+    case 6: return launch<6>(p, st);
+    case 8: return launch<8>(p, st);
+    case 10: return launch<10>(p, st);
+    case 12: return launch<12>(p, st);
+    case 14: return launch<14>(p, st);
+    default: return launch<16>(p, st);
+  }
+}

@@ -187,10 +187,15 @@ def test_window_attention_prompt_steps_and_portions(H, G, dk, dv, window, keep):
     want = O.diff_attention(q.double(), k.double(), v.double(), gate.double(), lam, H, G, dk, dv, 1.0 / math.sqrt(dk), window, keep, diff, 1e-5)
     for portions in ([T], [50] + [1] * 40, [2, 3, 30, 1, 4, 41, 2, 7]):
         _close(_attn_gpu(q, k, v, gate, H, G, dk, dv, window, keep, lam, diff, portions), want, 3e-5, f"portions {portions[:4]}")
-    _close(_attn_gpu(q, k, v, gate, H, G, dk, dv, window, keep, lam, diff, [33, 1, 1, 55], dtype=B16), want, 3e-2, "bf16")
+    # bf16 activations (the tensor-core kernel where the shape allows it): same inputs rounded to bf16 first, so only the
+    # kernel's own arithmetic and the bf16 rounding of its output remain
+    qb, kb, vb, gb = (_bf(t).float() for t in (q, k, v, gate))
+    want_b = O.diff_attention(qb.double(), kb.double(), vb.double(), gb.double(), lam, H, G, dk, dv, 1.0 / math.sqrt(dk), window, keep, diff, 1e-5)
+    for portions in ([T], [33, 1, 1, 55], [17, 16, 40, 17]):
+        _close(_attn_gpu(qb, kb, vb, gb, H, G, dk, dv, window, keep, lam, diff, portions, dtype=B16), want_b, 6e-3, f"bf16 {portions}")
 
 
-@pytest.mark.parametrize("mode", ["prompt", "steps"])
+@pytest.mark.parametrize("mode", ["prompt", "steps", "prompt_bf16"])
 def test_window_and_kept_token_edges_with_a_dominant_key(mode):
     """One key is given a score far above all others: the output must switch exactly where the mask says -- distance
     window-1 vs window, kept index keep-1 vs keep -- in a prompt and in single-token steps, across tile borders."""
@@ -204,11 +209,14 @@ def test_window_and_kept_token_edges_with_a_dominant_key(mode):
             q, k, v, gate = _attn_case(H, G, dk, dv, T, window, keep, seed=i * 1000 + j, spike=(i, j))
             gate[:] = 30.0                                  # gate -> 1
             want = O.diff_attention(q.double(), k.double(), v.double(), gate.double(), lam, H, G, dk, dv, 1.0 / math.sqrt(dk), window, keep, diff, 1e-5, rows=[i])
-            portions = [T] if mode == "prompt" else [i] + [1] * (T - i)
-            got = _attn_gpu(q, k, v, gate, H, G, dk, dv, window, keep, lam, diff, portions)
-            _close(got[i], want[i], 3e-5, f"query {i} key {j}")
+            portions = [i] + [1] * (T - i) if mode == "steps" else [T]
+            if mode == "prompt_bf16":
+                q, k, v, gate = (_bf(t).float() for t in (q, k, v, gate))
+                want = O.diff_attention(q.double(), k.double(), v.double(), gate.double(), lam, H, G, dk, dv, 1.0 / math.sqrt(dk), window, keep, diff, 1e-5, rows=[i])
+            got = _attn_gpu(q, k, v, gate, H, G, dk, dv, window, keep, lam, diff, portions, dtype=B16 if mode == "prompt_bf16" else F32)
+            _close(got[i], want[i], 3e-5 if mode != "prompt_bf16" else 6e-3, f"query {i} key {j}")
             seen = O.visible(i, j, window, keep)
-            picks = torch.allclose(want[i].float(), (O.rms(v[j].double(), 1e-5)).float(), atol=1e-3)
+            picks = torch.allclose(want[i].float(), (O.rms(v[j].double(), 1e-5)).float(), atol=1e-3) and torch.allclose(got[i].cpu(), O.rms(v[j].double(), 1e-5).float(), atol=2e-2)
             assert picks == seen, (i, j, seen)
 
 
