@@ -353,3 +353,19 @@ def test_greedy_generation_through_the_generator(device_loop):
         row = want[len(full) - n_new - 1 + s]
         assert row[picked[0, s]] >= row.max() - 2e-2, s
         _close(logits[0, s], row, 2e-5 if not device_loop else 1e-2, f"kept logits {s}")     # the device loop keeps the sampler's bf16 view of the logits
+
+
+def test_command_line_generates_from_a_checkpoint_folder(tmp_path, capsys):
+    """scripts/generate.py --model-dir: config.json picks the model class, the streaming loader fills it, generate() runs greedy."""
+    from tests.test_zaverax_host import _write_checkpoint
+    from scripts import generate as cli
+    cfg = O.make_config(**dict(CONFIGS["mixed"], vocab=512))
+    W = O.random_weights(cfg, seed=13)
+    _write_checkpoint(str(tmp_path / "ckpt"), cfg, W)
+    texts, scores = cli.main(["--model-dir", str(tmp_path / "ckpt"), "--prompt", "ACGTTGCA", "--n-samples", "2", "--n-tokens", "9", "--top-k", "1", "--device", DEV, "--verbose", "0"])
+    assert len(texts) == 2 and texts[0] == texts[1] and len(scores) == 2
+    ids = [ord(c) for c in "ACGTTGCA"]
+    want = O.forward(cfg, W, ids)
+    model = _model(cfg, W, B16)
+    first, _ = model(torch.tensor([ids], device=DEV))
+    assert first[0, -1].argmax().item() == want[-1].argmax().item() or want[-1].max() - want[-1][first[0, -1].argmax().item()] < 0.1
