@@ -47,4 +47,17 @@ elif what == "attn":
     qkv = torch.randn(B, L, 3, H, 128, device=dev).bfloat16()
     for _ in range(3):
         G._attn(qkv, B, L, H, 1)
+elif what == "zaverax":
+    # one forward of a 2-layer Zaverax model (recurrent + attention) at width 2048: every new kernel once per forward
+    from evo_b200.zaverax import Zaverax, ZaveraxConfig
+    rec = {"type": "hgrn2", "mixer": {"heads": 16, "dim": 128, "vdim": 128}, "mlp": {"kind": "dense", "ff": 5464}}
+    att = {"type": "attention", "mixer": {"heads": 16, "kv_heads": 16, "dim": 64, "vdim": 128, "scale": 0.125, "diff": 0.5, "mask": {"size": 1024, "keep_first": 16}},
+           "mlp": {"kind": "dense", "ff": 5464}}
+    zc = {"architecture": "Zaverax", "vocab": 512, "width": 2048, "layers": [rec, att], "norm": {"eps": 1e-5}, "canon": {"taps": 3},
+          "loop": {"start": 0, "stop": 0, "times": 1}, "residual_mult": 0.5, "logit_softcap": 15.0}
+    model = Zaverax(ZaveraxConfig.from_dict(zc)).init_random(0, device=dev)
+    ids = torch.randint(0, 512, (4, 4096), device=dev)
+    for _ in range(2):
+        model(ids)
+    torch.cuda.synchronize()
 print("done", what)
