@@ -30,7 +30,7 @@ template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = _
 constexpr int TCH = 16;      // tokens staged per round
 
 template <typename T, int RPT>
-__global__ void __launch_bounds__(RPT <= 16 ? 1024 : (RPT == 32 ? 512 : 256)) hgrn2_kernel(evo_hgrn2_params p, int KP, int dvp, float* __restrict__ raw) {
+__global__ void __launch_bounds__(RPT <= 16 ? 1024 : (RPT == 32 ? 512 : 256)) hgrn2_kernel(evo_hgrn2_params p, int KP, int dvp, float* __restrict__ raw, int4 steps) {
   extern __shared__ __align__(16) float smem[];
   const int dk = p.dk, dv = p.dv, dkp = KP * RPT;
   float2* fq = reinterpret_cast<float2*>(smem);            // [TCH][dkp]  (gate, activated query)
@@ -60,8 +60,8 @@ __global__ void __launch_bounds__(RPT <= 16 ? 1024 : (RPT == 32 ? 512 : 256)) hg
     const int nt = (int)min((int64_t)TCH, p.L - t0);
     const int64_t row0 = (int64_t)b * p.L + t0;
     __syncthreads();                                   // the previous round's read-outs have been folded
-    for (int i = tid; i < nt * dkp; i += nthr) {
-      const int tt = i / dkp, k = i % dkp;
+    // (token, channel) of this thread's first element; steps = blockDim / and % the row widths, from the host: no division inside the loops
+    for (int tt = tid / dkp, k = tid % dkp; tt < nt; ) {
       float2 e = make_float2(0.f, 0.f);
       if (k < dk) {
         const float l = __bfloat162float(lo[k]);
@@ -70,11 +70,14 @@ __global__ void __launch_bounds__(RPT <= 16 ? 1024 : (RPT == 32 ? 512 : 256)) hg
         e.x = l + (1.f - l) / (1.f + expf(-fr));
         e.y = qr / (1.f + expf(-qr));
       }
-      fq[i] = e;
+      fq[tt * dkp + k] = e;
+      tt += steps.x; k += steps.y;
+      if (k >= dkp) { k -= dkp; ++tt; }
     }
-    for (int i = tid; i < nt * dvp; i += nthr) {
-      const int tt = i / dvp, c = i % dvp;
-      vv[i] = j0 + c < dv ? ldf(vp + (row0 + tt) * p.ld + j0 + c) : 0.f;
+    for (int tt = tid / dvp, c = tid % dvp; tt < nt; ) {
+      vv[tt * dvp + c] = j0 + c < dv ? ldf(vp + (row0 + tt) * p.ld + j0 + c) : 0.f;
+      tt += steps.z; c += steps.w;
+      if (c >= dvp) { c -= dvp; ++tt; }
     }
     __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
@@ -161,6 +164,10 @@ inline Plan plan(int dk, int dv, int64_t ctas, int64_t L) {
       int chunks = 1;
       if (L >= 256 && ctas * 2 <= device_sm_count() && dvp >= 64) chunks = (int)std::min<int64_t>(dvp / 32, device_sm_count() / ctas);
       const int dvc = (dvp / 32 + chunks - 1) / chunks * 32;
+      // a split CTA has fewer value channels: give its threads fewer rows again so that it keeps as many warps
+      if (chunks > 1)
+        for (int r2 : {8, 16})
+          if (r2 < rpt && (int64_t)((dk + r2 - 1) / r2) * dvc <= 1024) return {r2, (dk + r2 - 1) / r2, dvc, (dv + dvc - 1) / dvc};
       return {rpt, KP, dvc, (dv + dvc - 1) / dvc};
     }
   }
@@ -175,7 +182,8 @@ int launch(const evo_hgrn2_params* p, int KP, int dvp, int chunks, float* raw, c
   const size_t smem = sizeof(float) * ((size_t)2 * TCH * KP * RPT + (size_t)TCH * dvp + (size_t)TCH * KP * dvp);
   auto kern = hgrn2_kernel<T, RPT>;
   if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<dim3(p->H, p->B, chunks), dim3(KP * dvp), smem, st>>>(*p, KP, dvp, raw);
+  const int nthr = KP * dvp, dkp = KP * RPT;
+  kern<<<dim3(p->H, p->B, chunks), dim3(nthr), smem, st>>>(*p, KP, dvp, raw, make_int4(nthr / dkp, nthr % dkp, nthr / dvp, nthr % dvp));
   int rc = check_launch("evo_hgrn2_fwd");
   if (rc || !raw) return rc;
   const int64_t warps = (int64_t)p->B * p->L * p->H;

@@ -268,8 +268,15 @@ class Zaverax(KernelOps, nn.Module):
             cache = ip.key_value_memory_dict.get(r)
             if cache is None:
                 cache = ip.key_value_memory_dict[r] = torch.zeros(ip.max_batch_size, ip.max_seqlen, kw + vw, dtype=self.act_dtype, device=dev)
-            if B > cache.shape[0] or off + L > cache.shape[1]:
-                raise _lib.EvoError(f"KV cache too small: batch {B} > {cache.shape[0]} or length {off + L} > {cache.shape[1]}")
+            if B > cache.shape[0]:
+                raise _lib.EvoError(f"KV cache too small: batch {B} > {cache.shape[0]}")
+            if off + L > cache.shape[1]:
+                if pos_dev is not None:             # inside a captured step the cache cannot move
+                    raise _lib.EvoError(f"KV cache too small: length {off + L} > {cache.shape[1]}")
+                grown = torch.zeros(cache.shape[0], max(off + L, 2 * cache.shape[1]), kw + vw, dtype=self.act_dtype, device=dev)
+                grown[:, :off] = cache[:, :off]
+                cache = ip.key_value_memory_dict[r] = grown
+                ip.max_seqlen = max(ip.max_seqlen, cache.shape[1])
             cw = kw + vw
             check(lib.evo_copy_rows(C.c_void_p(z.data_ptr() + qw * esz), ld, ptr(cache), cw, cache.shape[1] * cw, B, L, cw, off,
                                     ptr(pos_dev), self._dt, self._stream()), "evo_copy_rows")
