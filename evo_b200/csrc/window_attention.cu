@@ -28,6 +28,25 @@ template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return _
 template <typename T> __device__ __forceinline__ void stf(T* p, float v);
 template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+// 16 bytes of a row as floats (EV = 16 / sizeof(T) elements), and 4 consecutive elements (8 bytes of bf16, 16 of fp32)
+template <typename T> struct Row16;
+template <> struct Row16<float> {
+  static constexpr int EV = 4;
+  static __device__ __forceinline__ void load(const float* p, float* o) { const float4 u = *reinterpret_cast<const float4*>(p); o[0] = u.x; o[1] = u.y; o[2] = u.z; o[3] = u.w; }
+  static __device__ __forceinline__ void load4(const float* p, float* o) { load(p, o); }
+};
+template <> struct Row16<bf16> {
+  static constexpr int EV = 8;
+  static __device__ __forceinline__ void unpack(uint32_t u, float& a, float& b) { a = __uint_as_float(u << 16); b = __uint_as_float(u & 0xffff0000u); }
+  static __device__ __forceinline__ void load(const bf16* p, float* o) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    unpack(u.x, o[0], o[1]); unpack(u.y, o[2], o[3]); unpack(u.z, o[4], o[5]); unpack(u.w, o[6], o[7]);
+  }
+  static __device__ __forceinline__ void load4(const bf16* p, float* o) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    unpack(u.x, o[0], o[1]); unpack(u.y, o[2], o[3]);
+  }
+};
 
 constexpr int QT = 8;        // warps per CTA
 constexpr int KT = 32;       // keys per tile (one per lane)
@@ -81,7 +100,8 @@ __device__ __forceinline__ bool tile_scores(Softmax<NM, MAXCV>& sm, const float*
 }
 
 // combination of the maps, head norm, gate, store (one warp = one query row)
-template <typename T, int NM, int MAXCV>
+// BLOCKED: accumulator c of a lane is channel lane * MAXCV + c (the vector path of the few-query kernel), else lane + 32 * c
+template <typename T, int NM, int MAXCV, bool BLOCKED = false>
 __device__ __forceinline__ void finish_row(const evo_window_attn_params& p, const Softmax<NM, MAXCV>& sm, int64_t row, int h, int lane) {
   const int dv = p.dv;
   float o[MAXCV];
@@ -90,7 +110,7 @@ __device__ __forceinline__ void finish_row(const evo_window_attn_params& p, cons
   for (int c = 0; c < MAXCV; ++c) {
     float v = sm.acc[0][c] / sm.l[0];
     if (NM == 2) v -= p.lambda * (sm.acc[NM - 1][c] / sm.l[NM - 1]);
-    o[c] = (lane + 32 * c < dv) ? v : 0.f;
+    o[c] = ((BLOCKED ? lane * MAXCV + c : lane + 32 * c) < dv) ? v : 0.f;
     ss = fmaf(o[c], o[c], ss);
   }
   float mul = 1.f;
@@ -99,7 +119,7 @@ __device__ __forceinline__ void finish_row(const evo_window_attn_params& p, cons
   const T* grow = p.gate ? (const T*)p.gate + row * p.gate_tok_stride + h * dv : nullptr;
 #pragma unroll
   for (int c = 0; c < MAXCV; ++c) {
-    const int ch = lane + 32 * c;
+    const int ch = BLOCKED ? lane * MAXCV + c : lane + 32 * c;
     if (ch < dv) {
       float v = o[c] * mul;
       if (grow) v *= 1.f / (1.f + expf(-ldf(grow + ch)));
@@ -178,7 +198,9 @@ __global__ void __launch_bounds__(QT * 32) window_attn_kernel(evo_window_attn_pa
 }
 
 // ---- few queries: one CTA per (query, head); its warps take the key tiles round-robin, straight from global memory
-template <typename T, int NM, int MAXCV>
+// VEC (head sizes, strides and bases allow 16-byte key loads and 4-channel value loads): same sums in the same order, fewer and
+// wider loads -- the step is bound by streaming the window's keys and values once
+template <typename T, int NM, int MAXCV, bool VEC>
 __global__ void __launch_bounds__(QT * 32) window_attn_split_kernel(evo_window_attn_params p) {
   extern __shared__ float smem[];
   const int dk = p.dk, dv = p.dv, kw = NM * dk;
@@ -211,7 +233,18 @@ __global__ void __launch_bounds__(QT * 32) window_attn_split_kernel(evo_window_a
 #pragma unroll
     for (int a = 0; a < NM; ++a) {
       float d = 0.f;
-      for (int e = 0; e < dk; ++e) d = fmaf(Qs[a * dk + e], ldf(krow + a * dk + e), d);
+      if (VEC) {
+        constexpr int EV = Row16<T>::EV;
+#pragma unroll 4
+        for (int e = 0; e < dk; e += EV) {
+          float kv[EV];
+          Row16<T>::load(krow + a * dk + e, kv);
+#pragma unroll
+          for (int u = 0; u < EV; ++u) d = fmaf(Qs[a * dk + e + u], kv[u], d);
+        }
+      } else {
+        for (int e = 0; e < dk; ++e) d = fmaf(Qs[a * dk + e], ldf(krow + a * dk + e), d);
+      }
       s[a] = vis ? d * p.scale : -INFINITY;
     }
 #pragma unroll
@@ -223,6 +256,28 @@ __global__ void __launch_bounds__(QT * 32) window_attn_split_kernel(evo_window_a
       sm.m[a] = mn;
 #pragma unroll
       for (int c = 0; c < MAXCV; ++c) sm.acc[a][c] *= corr;
+    }
+    if (VEC) {
+      const bool mine = lane * MAXCV < dv;             // dv % 4 == 0: a lane's groups of 4 channels are inside the head or outside
+#pragma unroll 8
+      for (int r = 0; r < nk; ++r) {
+        float pr[NM];
+#pragma unroll
+        for (int a = 0; a < NM; ++a) pr[a] = __shfl_sync(0xffffffffu, pm[a], r);
+        const T* vrow = vb + (k0 + r) * p.v_tok_stride + lane * MAXCV;
+#pragma unroll
+        for (int c = 0; c < MAXCV; c += 4) {
+          if (mine && lane * MAXCV + c < dv) {
+            float vv[4];
+            Row16<T>::load4(vrow + c, vv);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+              for (int a = 0; a < NM; ++a) sm.acc[a][c + u] = fmaf(pr[a], vv[u], sm.acc[a][c + u]);
+          }
+        }
+      }
+      continue;
     }
     for (int r = 0; r < nk; ++r) {
       float pr[NM];
@@ -266,7 +321,7 @@ __global__ void __launch_bounds__(QT * 32) window_attn_split_kernel(evo_window_a
       for (int c = 0; c < MAXCV; ++c) tot.acc[a][c] = fmaf(src[2 + lane + 32 * c], sc, tot.acc[a][c]);
     }
   }
-  finish_row<T, NM, MAXCV>(p, tot, row, h, lane);
+  finish_row<T, NM, MAXCV, VEC>(p, tot, row, h, lane);
 }
 
 template <typename T, int NM, int MAXCV>
@@ -274,7 +329,11 @@ int launch_cv(const evo_window_attn_params* p, cudaStream_t st) {
   const int kw = NM * p->dk;
   if (p->Lq <= 4) {
     const size_t smem = sizeof(float) * ((size_t)kw + (size_t)QT * NM * (2 + MAXCV * 32));
-    auto kern = window_attn_split_kernel<T, NM, MAXCV>;
+    constexpr int EV = Row16<T>::EV;
+    auto a16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
+    const bool vec = p->dk % EV == 0 && p->dv % 4 == 0 && p->k_tok_stride % EV == 0 && p->k_batch_stride % EV == 0 && p->v_tok_stride % EV == 0 &&
+                     p->v_batch_stride % EV == 0 && a16(p->k) && a16(p->v);
+    auto kern = vec ? window_attn_split_kernel<T, NM, MAXCV, true> : window_attn_split_kernel<T, NM, MAXCV, false>;
     if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<dim3((unsigned)p->Lq, p->H, p->B), QT * 32, smem, st>>>(*p);
   } else {

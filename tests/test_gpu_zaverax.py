@@ -195,7 +195,7 @@ def test_window_attention_prompt_steps_and_portions(H, G, dk, dv, window, keep):
         _close(_attn_gpu(qb, kb, vb, gb, H, G, dk, dv, window, keep, lam, diff, portions, dtype=B16), want_b, 6e-3, f"bf16 {portions}")
 
 
-@pytest.mark.parametrize("mode", ["prompt", "steps", "prompt_bf16"])
+@pytest.mark.parametrize("mode", ["prompt", "steps", "prompt_bf16", "steps_bf16"])
 def test_window_and_kept_token_edges_with_a_dominant_key(mode):
     """One key is given a score far above all others: the output must switch exactly where the mask says -- distance
     window-1 vs window, kept index keep-1 vs keep -- in a prompt and in single-token steps, across tile borders."""
@@ -209,12 +209,12 @@ def test_window_and_kept_token_edges_with_a_dominant_key(mode):
             q, k, v, gate = _attn_case(H, G, dk, dv, T, window, keep, seed=i * 1000 + j, spike=(i, j))
             gate[:] = 30.0                                  # gate -> 1
             want = O.diff_attention(q.double(), k.double(), v.double(), gate.double(), lam, H, G, dk, dv, 1.0 / math.sqrt(dk), window, keep, diff, 1e-5, rows=[i])
-            portions = [i] + [1] * (T - i) if mode == "steps" else [T]
-            if mode == "prompt_bf16":
+            portions = [i] + [1] * (T - i) if mode.startswith("steps") else [T]
+            if mode.endswith("bf16"):
                 q, k, v, gate = (_bf(t).float() for t in (q, k, v, gate))
                 want = O.diff_attention(q.double(), k.double(), v.double(), gate.double(), lam, H, G, dk, dv, 1.0 / math.sqrt(dk), window, keep, diff, 1e-5, rows=[i])
-            got = _attn_gpu(q, k, v, gate, H, G, dk, dv, window, keep, lam, diff, portions, dtype=B16 if mode == "prompt_bf16" else F32)
-            _close(got[i], want[i], 3e-5 if mode != "prompt_bf16" else 6e-3, f"query {i} key {j}")
+            got = _attn_gpu(q, k, v, gate, H, G, dk, dv, window, keep, lam, diff, portions, dtype=B16 if mode.endswith("bf16") else F32)
+            _close(got[i], want[i], 3e-5 if not mode.endswith("bf16") else 6e-3, f"query {i} key {j}")
             seen = O.visible(i, j, window, keep)
             picks = torch.allclose(want[i].float(), (O.rms(v[j].double(), 1e-5)).float(), atol=1e-3) and torch.allclose(got[i].cpu(), O.rms(v[j].double(), 1e-5).float(), atol=2e-2)
             assert picks == seen, (i, j, seen)
