@@ -50,6 +50,7 @@ template <> struct Row16<bf16> {
 
 constexpr int QT = 8;        // warps per CTA
 constexpr int KT = 32;       // keys per tile (one per lane)
+constexpr int QS_MAX = 16;   // most warps of the few-query kernel
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -201,18 +202,18 @@ __global__ void __launch_bounds__(QT * 32) window_attn_kernel(evo_window_attn_pa
 // VEC (head sizes, strides and bases allow 16-byte key loads and 4-channel value loads): same sums in the same order, fewer and
 // wider loads -- the step is bound by streaming the window's keys and values once
 template <typename T, int NM, int MAXCV, bool VEC>
-__global__ void __launch_bounds__(QT * 32) window_attn_split_kernel(evo_window_attn_params p) {
+__global__ void __launch_bounds__(QS_MAX * 32) window_attn_split_kernel(evo_window_attn_params p) {
   extern __shared__ float smem[];
   const int dk = p.dk, dv = p.dv, kw = NM * dk;
   float* Qs = smem;                                   // [kw]
-  float* Mg = Qs + kw;                                // [QT][NM][2 + dvp] partial (max, sum, acc)
+  float* Mg = Qs + kw;                                // [warps][NM][2 + dvp] partial (max, sum, acc)
   const int dvp = MAXCV * 32;
   const int b = blockIdx.z, h = blockIdx.y, g = h / (p.H / p.G);
-  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const int64_t pos = p.pos_dev ? (int64_t)*p.pos_dev : p.q_pos0;
   const int64_t rel = blockIdx.x, i = pos + rel, row = (int64_t)b * p.Lq + rel;
   const T* q = (const T*)p.q + row * p.q_tok_stride + (int64_t)h * kw;
-  for (int e = threadIdx.x; e < kw; e += QT * 32) Qs[e] = ldf(q + e);
+  for (int e = threadIdx.x; e < kw; e += blockDim.x) Qs[e] = ldf(q + e);
   __syncthreads();
   const T* kb = (const T*)p.k + (int64_t)b * p.k_batch_stride + (int64_t)g * kw;
   const T* vb = (const T*)p.v + (int64_t)b * p.v_batch_stride + (int64_t)g * dv;
@@ -223,7 +224,7 @@ __global__ void __launch_bounds__(QT * 32) window_attn_split_kernel(evo_window_a
 
   Softmax<NM, MAXCV> sm;
   sm.init();
-  for (int64_t t = w; t < n_keep + n_win; t += QT) {
+  for (int64_t t = w; t < n_keep + n_win; t += nw) {
     const int64_t k0 = t < n_keep ? t * KT : win_lo + (t - n_keep) * KT;
     const int64_t hi = t < n_keep ? keep_hi : i + 1;
     const int nk = (int)min((int64_t)KT, hi - k0);
@@ -310,9 +311,9 @@ __global__ void __launch_bounds__(QT * 32) window_attn_split_kernel(evo_window_a
 #pragma unroll
   for (int a = 0; a < NM; ++a) {
     float mx = -INFINITY;
-    for (int ww = 0; ww < QT; ++ww) mx = fmaxf(mx, Mg[(ww * NM + a) * (2 + dvp)]);
+    for (int ww = 0; ww < nw; ++ww) mx = fmaxf(mx, Mg[(ww * NM + a) * (2 + dvp)]);
     tot.m[a] = mx;
-    for (int ww = 0; ww < QT; ++ww) {
+    for (int ww = 0; ww < nw; ++ww) {
       const float* src = Mg + (ww * NM + a) * (2 + dvp);
       if (src[0] == -INFINITY) continue;              // this warp saw no tile
       const float sc = expf(src[0] - mx);
@@ -328,14 +329,18 @@ template <typename T, int NM, int MAXCV>
 int launch_cv(const evo_window_attn_params* p, cudaStream_t st) {
   const int kw = NM * p->dk;
   if (p->Lq <= 4) {
-    const size_t smem = sizeof(float) * ((size_t)kw + (size_t)QT * NM * (2 + MAXCV * 32));
+    // the warps of a CTA take the query's key tiles in turn; each tile is a chain of dependent loads (keys -> weights -> values), so
+    // a long window gets more warps: shorter chains and more bytes in flight
+    const int64_t span = p->window > 0 ? (int64_t)p->window + p->keep_first : (p->pos_dev ? (int64_t)1 << 30 : p->q_pos0 + p->Lq);
+    const int warps = span >= 24 * KT ? QS_MAX : QT;
+    const size_t smem = sizeof(float) * ((size_t)kw + (size_t)warps * NM * (2 + MAXCV * 32));
     constexpr int EV = Row16<T>::EV;
     auto a16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
     const bool vec = p->dk % EV == 0 && p->dv % 4 == 0 && p->k_tok_stride % EV == 0 && p->k_batch_stride % EV == 0 && p->v_tok_stride % EV == 0 &&
                      p->v_batch_stride % EV == 0 && a16(p->k) && a16(p->v);
     auto kern = vec ? window_attn_split_kernel<T, NM, MAXCV, true> : window_attn_split_kernel<T, NM, MAXCV, false>;
     if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<dim3((unsigned)p->Lq, p->H, p->B), QT * 32, smem, st>>>(*p);
+    kern<<<dim3((unsigned)p->Lq, p->H, p->B), warps * 32, smem, st>>>(*p);
   } else {
     const size_t smem = sizeof(float) * ((size_t)KT * (kw + 1) + (size_t)KT * p->dv + (size_t)QT * kw);
     EVO_REQUIRE(smem <= 227 * 1024, "evo_window_attn_fwd: head too wide for shared memory (%zu bytes)", smem);

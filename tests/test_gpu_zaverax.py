@@ -220,6 +220,24 @@ def test_window_and_kept_token_edges_with_a_dominant_key(mode):
             assert picks == seen, (i, j, seen)
 
 
+@pytest.mark.parametrize("dtype", [F32, B16])
+def test_long_window_single_steps(dtype):
+    """A window of several hundred keys: the single-token kernel spreads its key tiles over more warps.  One far key, exactly at
+    the window's edge for the last query and one past it for the query after, dominates where it is visible."""
+    H, G, dk, dv, window, keep = 2, 1, 16, 32, 800, 3
+    T, lam, diff = 860, 0.4, 0.25
+    i = 840
+    q, k, v, gate = _attn_case(H, G, dk, dv, T, window, keep, seed=11, spike=(i, i - window + 1))
+    q[i + 1, :2 * dk] = q[i, :2 * dk]                       # the next query asks for the same key, now one step outside
+    if dtype == B16:
+        q, k, v, gate = (_bf(t).float() for t in (q, k, v, gate))
+    rows = list(range(820, T))
+    want = O.diff_attention(q.double(), k.double(), v.double(), gate.double(), lam, H, G, dk, dv, 1.0 / math.sqrt(dk), window, keep, diff, 1e-5, rows=rows)
+    got = _attn_gpu(q, k, v, gate, H, G, dk, dv, window, keep, lam, diff, [820] + [1] * (T - 820), dtype=dtype)
+    _close(got[820:], want[820:], 3e-5 if dtype == F32 else 6e-3, "steps behind a long window")
+    assert (want[i, :dv] - want[i + 1, :dv]).abs().max() > 0.1          # the edge shows in the expected values
+
+
 # ------------------------------------------------------------------ the model
 def _model(cfg, W, dtype=F32):
     from evo_b200.zaverax import Zaverax, ZaveraxConfig
