@@ -48,7 +48,7 @@ __device__ __forceinline__ void split_pack(float x, float y, uint32_t& hi, uint3
 
 // NV8 = padded dv / 8 (output tiles of 8 channels per warp row block)
 template <int NV8>
-__global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_attn_params p, int dkp, int qst, int kst, int vst, int vec) {
+__global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_attn_params p, int dkp, int qst, int kst, int vst, int vec, int2 vstep) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [WARPS*16][qst]   both maps' queries
   bf16* Ks = Qs + WARPS * QROWS * qst;                           // [KT][kst]         both maps' keys
@@ -58,17 +58,21 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, qr = lane >> 2, qc = (lane & 3) * 2;
   const int64_t pos = p.pos_dev ? (int64_t)*p.pos_dev : p.q_pos0;
   const int64_t rel0 = (int64_t)blockIdx.x * (WARPS * QROWS);
+  // 16-byte copies of [row][both maps' dkp columns]: a row has c8n chunks, cpm per map; this thread's first (row, chunk) and its step
+  // (vstep = 128 / c8n, 128 % c8n, from the host) replace a division per copy
+  const int cpm = dkp / 8, c8n = 2 * cpm, vr0 = tid / c8n, vc0 = tid % c8n;
   const bf16* qg = (const bf16*)p.q;
   // queries of the CTA: [row][map][dkp], zero padding for rows past Lq and columns past dk
   const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
   if (vec) {                              // dk, dv, strides multiples of 8 and 16-byte aligned bases: 8 elements per copy
-    const int c8n = 2 * dkp / 8;
-    for (int idx = tid; idx < WARPS * QROWS * c8n; idx += WARPS * 32) {
-      const int r = idx / c8n, c = (idx % c8n) * 8, m = c / dkp, e = c % dkp;
+    for (int r = vr0, cc = vc0; r < WARPS * QROWS; ) {
+      const int m = cc >= cpm, e = (cc - m * cpm) * 8;
       const int64_t rel = rel0 + r;
       uint4 v = zero4;
       if (rel < p.Lq && e < dk) v = *reinterpret_cast<const uint4*>(qg + ((int64_t)b * p.Lq + rel) * p.q_tok_stride + (int64_t)h * 2 * dk + m * dk + e);
-      *reinterpret_cast<uint4*>(Qs + r * qst + c) = v;
+      *reinterpret_cast<uint4*>(Qs + r * qst + cc * 8) = v;
+      r += vstep.x; cc += vstep.y;
+      if (cc >= c8n) { cc -= c8n; ++r; }
     }
   } else {
     for (int idx = tid; idx < WARPS * QROWS * 2 * dkp; idx += WARPS * 32) {
@@ -106,12 +110,13 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
       const int nk = (int)min((int64_t)KT, hi - k0);
       __syncthreads();
       if (vec) {
-        const int c8n = 2 * dkp / 8;
-        for (int idx = tid; idx < KT * c8n; idx += WARPS * 32) {
-          const int r = idx / c8n, c = (idx % c8n) * 8, m = c / dkp, e = c % dkp;
+        for (int r = vr0, cc = vc0; r < KT; ) {
+          const int m = cc >= cpm, e = (cc - m * cpm) * 8;
           uint4 v = zero4;
           if (r < nk && e < dk) v = *reinterpret_cast<const uint4*>(kb + (k0 + r) * p.k_tok_stride + m * dk + e);
-          *reinterpret_cast<uint4*>(Ks + r * kst + c) = v;
+          *reinterpret_cast<uint4*>(Ks + r * kst + cc * 8) = v;
+          r += vstep.x; cc += vstep.y;
+          if (cc >= c8n) { cc -= c8n; ++r; }
         }
         for (int idx = tid; idx < KT * NV8; idx += WARPS * 32) {
           const int r = idx / NV8, c = (idx % NV8) * 8;
@@ -263,7 +268,9 @@ int launch(const evo_window_attn_params* p, cudaStream_t st) {
                   p->k_batch_stride % 8 == 0 && p->v_batch_stride % 8 == 0 && a16(p->q) && a16(p->k) && a16(p->v);
   auto kern = window_attn_mma_kernel<NV8>;
   if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<dim3((unsigned)((p->Lq + WARPS * QROWS - 1) / (WARPS * QROWS)), p->H, p->B), WARPS * 32, smem, st>>>(*p, dkp, qst, kst, vst, vec);
+  const int c8n = 2 * dkp / 8;
+  kern<<<dim3((unsigned)((p->Lq + WARPS * QROWS - 1) / (WARPS * QROWS)), p->H, p->B), WARPS * 32, smem, st>>>(*p, dkp, qst, kst, vst, vec,
+                                                                                                                 make_int2(WARPS * 32 / c8n, WARPS * 32 % c8n));
   return check_launch("evo_window_attn_fwd");
 }
 

@@ -103,7 +103,7 @@ def test_gemm_simt(M, N, K, dtype):
     _close(c[:, :N], a[:, :K].double() @ w[:, :K].double().T, 1e-5 if dtype == F32 else 6e-3, "gemm")
 
 
-@pytest.mark.parametrize("H,dk,dv", [(2, 12, 40), (1, 48, 64), (3, 130, 96), (1, 256, 320), (2, 7, 5)])
+@pytest.mark.parametrize("H,dk,dv", [(2, 12, 40), (1, 56, 64), (3, 130, 96), (1, 256, 320), (2, 7, 5)])
 def test_hgrn2_scan_step_and_carried_state(H, dk, dv):
     """whole sequence == portions (2, 1 and 17 tokens among them) through the carried state == the oracle; heads too large for
     one CTA take the split path."""
@@ -179,7 +179,7 @@ def _attn_gpu(q, k, v, gate, H, G, dk, dv, window, keep, lam, diff, portions, dt
     return torch.cat(outs, 0)
 
 
-@pytest.mark.parametrize("H,G,dk,dv,window,keep", [(3, 1, 20, 24, 9, 3), (4, 2, 48, 96, 40, 5), (2, 2, 8, 130, 33, 0), (1, 1, 64, 300, 5, 12), (2, 1, 16, 32, 64, 32), (2, 2, 12, 16, 0, 0)])
+@pytest.mark.parametrize("H,G,dk,dv,window,keep", [(3, 1, 20, 24, 9, 3), (4, 2, 40, 88, 40, 5), (2, 2, 8, 130, 33, 0), (1, 1, 64, 300, 5, 12), (2, 1, 16, 32, 64, 32), (2, 2, 12, 16, 0, 0)])
 def test_window_attention_prompt_steps_and_portions(H, G, dk, dv, window, keep):
     T = 90
     q, k, v, gate = _attn_case(H, G, dk, dv, T, window, keep, seed=dk)
