@@ -30,7 +30,7 @@ template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = _
 constexpr int TCH = 16;      // tokens staged per round
 
 template <typename T, int RPT>
-__global__ void __launch_bounds__(RPT <= 16 ? 1024 : (RPT == 32 ? 512 : 256)) hgrn2_kernel(evo_hgrn2_params p, int KP, int dvp, float* __restrict__ raw, int4 steps) {
+__global__ void __launch_bounds__(RPT <= 16 ? 1024 : (RPT == 32 ? 512 : 256), 1) hgrn2_kernel(evo_hgrn2_params p, int KP, int dvp, float* __restrict__ raw, int4 steps) {
   extern __shared__ __align__(16) float smem[];
   const int dk = p.dk, dv = p.dv, dkp = KP * RPT;
   float2* fq = reinterpret_cast<float2*>(smem);            // [TCH][dkp]  (gate, activated query)

@@ -288,6 +288,25 @@ def test_model_whole_steps_and_portions_match_the_oracle_in_fp32(name):
     _close(_portions(model, tokens, [2, 2, 3, 30, 1, 2, 17, 9, 2, 5, 2]), want, 2e-5, f"{name}: portions")
 
 
+def test_layers_with_their_own_sizes_and_a_cache_that_has_to_grow():
+    """Every layer brings its own head counts, head sizes, window and feed-forward width (one has none); the KV cache starts
+    smaller than the request and grows while the request runs."""
+    cfg = O.make_config(layers=("attention", "hgrn2", "attention", "hgrn2"), loop=(1, 3, 2), width=104, vocab=211, taps=2)
+    cfg["layers"][2]["mixer"] = {"heads": 4, "kv_heads": 4, "dim": 8, "vdim": 40, "scale": 0.2, "diff": 0.6, "mask": {"size": 3, "keep_first": 9}}
+    cfg["layers"][3]["mixer"] = {"heads": 5, "dim": 24, "vdim": 8}
+    cfg["layers"][1]["mlp"] = None
+    cfg["layers"][2]["mlp"]["ff"] = 72
+    W = O.random_weights(cfg, seed=21)
+    tokens = torch.randint(0, cfg["vocab"], (70,), generator=torch.Generator().manual_seed(8)).tolist()
+    want = O.forward(cfg, W, tokens)
+    model = _model(cfg, W)
+    got, _ = model(torch.tensor([tokens], device=DEV))
+    _close(got[0], want, 2e-5, "whole")
+    state = model.initialize_inference_params(max_seqlen=16, max_batch_size=1)
+    _close(_portions(model, tokens, [9, 2, 20, 1, 1, 30, 7], state=state), want, 2e-5, "portions through a growing cache")
+    assert all(c.shape[1] >= 70 for c in state["mha"].key_value_memory_dict.values())
+
+
 def test_model_bf16_stays_within_rounding_of_the_oracle_and_of_itself():
     cfg = O.make_config(**CONFIGS["mixed"])
     W = O.random_weights(cfg, seed=3)
