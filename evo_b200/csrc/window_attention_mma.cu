@@ -39,6 +39,12 @@ __device__ __forceinline__ float quad_sum(float v) {
   v += __shfl_xor_sync(0xffffffffu, v, 1);
   return v + __shfl_xor_sync(0xffffffffu, v, 2);
 }
+// 2^x for x <= 0 (softmax weights): the bare instruction; results below 2^-126 flush to zero
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 // bf16 high part and bf16 residual of two probabilities
 __device__ __forceinline__ void split_pack(float x, float y, uint32_t& hi, uint32_t& lo) {
   const bf16 xh = __float2bfloat16_rn(x), yh = __float2bfloat16_rn(y);
@@ -143,6 +149,7 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
       const int64_t t_lo = k0, t_hi = k0 + nk - 1;
       if (t_lo > wi_hi) continue;
       if (windowed && wi_lo - t_hi >= p.window && t_lo >= p.keep_first) continue;
+      const bool full = nk == KT && t_hi <= wi_lo && (!windowed || wi_hi - t_lo < p.window || t_hi < p.keep_first);
 
 #pragma unroll
       for (int m = 0; m < 2; ++m) {
@@ -165,6 +172,17 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
         }
         // mask, running max / sum, probabilities
         float mx0 = -INFINITY, mx1 = -INFINITY;
+        if (full) {                                    // every key of the tile is visible to every row of the warp: no mask
+#pragma unroll
+          for (int n = 0; n < KT / 8; ++n) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const float s = Pm[0][n][c] * scale2;
+              Pm[0][n][c] = s;
+              if (c < 2) mx0 = fmaxf(mx0, s); else mx1 = fmaxf(mx1, s);
+            }
+          }
+        } else
 #pragma unroll
         for (int n = 0; n < KT / 8; ++n) {
 #pragma unroll
@@ -181,12 +199,12 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
         const float mn0 = fmaxf(mrun[m][0], mx0), mn1 = fmaxf(mrun[m][1], mx1);
         // rows that have seen no key yet keep max = -inf: use 0 as the reference so that exp() gives 0, not NaN
         const float r0 = mn0 == -INFINITY ? 0.f : mn0, r1 = mn1 == -INFINITY ? 0.f : mn1;
-        const float c0 = exp2f(mrun[m][0] - r0), c1 = exp2f(mrun[m][1] - r1);
+        const float c0 = ex2(mrun[m][0] - r0), c1 = ex2(mrun[m][1] - r1);
         float s0 = 0.f, s1 = 0.f;
 #pragma unroll
         for (int n = 0; n < KT / 8; ++n) {
-          Pm[0][n][0] = exp2f(Pm[0][n][0] - r0); Pm[0][n][1] = exp2f(Pm[0][n][1] - r0);
-          Pm[0][n][2] = exp2f(Pm[0][n][2] - r1); Pm[0][n][3] = exp2f(Pm[0][n][3] - r1);
+          Pm[0][n][0] = ex2(Pm[0][n][0] - r0); Pm[0][n][1] = ex2(Pm[0][n][1] - r0);
+          Pm[0][n][2] = ex2(Pm[0][n][2] - r1); Pm[0][n][3] = ex2(Pm[0][n][3] - r1);
           s0 += Pm[0][n][0] + Pm[0][n][1]; s1 += Pm[0][n][2] + Pm[0][n][3];
         }
         lrun[m][0] = lrun[m][0] * c0 + quad_sum(s0); lrun[m][1] = lrun[m][1] * c1 + quad_sum(s1);
