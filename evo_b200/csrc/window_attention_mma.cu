@@ -31,6 +31,10 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, const void* smem_
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem_row)));
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const void* smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem_row)));
+}
 __device__ __forceinline__ float quad_max(float v) {
   v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
   return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
@@ -165,9 +169,11 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
           a[2] = *reinterpret_cast<const uint32_t*>(qa + qr * qst + 8);
           a[3] = *reinterpret_cast<const uint32_t*>(qa + (qr + 8) * qst + 8);
 #pragma unroll
-          for (int n = 0; n < KT / 8; ++n) {
-            const bf16* kbp = Ks + (n * 8 + qr) * kst + m * dkp + ks * 16 + qc;
-            mma_bf16(Pm[0][n], a, *reinterpret_cast<const uint32_t*>(kbp), *reinterpret_cast<const uint32_t*>(kbp + 8));
+          for (int n = 0; n < KT / 8; n += 2) {
+            uint32_t kf[4];            // b0, b1 of key tile n, then of tile n + 1: rows = keys, 8 features per 16-byte row
+            ldmatrix_x4(kf, Ks + ((n + (lane >> 4)) * 8 + (lane & 7)) * kst + m * dkp + ks * 16 + ((lane >> 3) & 1) * 8);
+            mma_bf16(Pm[0][n], a, kf[0], kf[1]);
+            mma_bf16(Pm[0][n + 1], a, kf[2], kf[3]);
           }
         }
         // mask, running max / sum, probabilities
@@ -208,9 +214,12 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
           s0 += Pm[0][n][0] + Pm[0][n][1]; s1 += Pm[0][n][2] + Pm[0][n][3];
         }
         lrun[m][0] = lrun[m][0] * c0 + quad_sum(s0); lrun[m][1] = lrun[m][1] * c1 + quad_sum(s1);
+        const bool moved = !__all_sync(0xffffffffu, mn0 == mrun[m][0] && mn1 == mrun[m][1]);
         mrun[m][0] = mn0; mrun[m][1] = mn1;
+        if (moved) {                                   // some row's maximum moved; otherwise c0 = c1 = 1 (or the row is still empty)
 #pragma unroll
-        for (int n = 0; n < NV8; ++n) { O[m][n][0] *= c0; O[m][n][1] *= c0; O[m][n][2] *= c1; O[m][n][3] *= c1; }
+          for (int n = 0; n < NV8; ++n) { O[m][n][0] *= c0; O[m][n][1] *= c0; O[m][n][2] *= c1; O[m][n][3] *= c1; }
+        }
         // O_m += P_m . V: high and low bf16 parts of P against the same V fragments (ldmatrix, transposed on the way)
 #pragma unroll
         for (int kk = 0; kk < KT / 16; ++kk) {
