@@ -95,7 +95,38 @@ class WindowAttnParams(C.Structure):
                 ("out", C.c_void_p), ("ldo", C.c_int64), ("dtype", C.c_int),
                 ("B", C.c_int), ("Lq", C.c_int64), ("H", C.c_int), ("G", C.c_int), ("dk", C.c_int), ("dv", C.c_int), ("n_maps", C.c_int),
                 ("q_pos0", C.c_int64), ("pos_dev", C.c_void_p), ("window", C.c_int64), ("keep_first", C.c_int64),
-                ("scale", C.c_float), ("lambda_", C.c_float), ("head_norm", C.c_int), ("norm_eps", C.c_float), ("out_scale", C.c_float)]
+                ("scale", C.c_float), ("lambda_", C.c_float), ("head_norm", C.c_int), ("norm_eps", C.c_float), ("out_scale", C.c_float), ("gate_per_head", C.c_int)]
+
+
+class BranchNormParams(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("y", C.c_void_p), ("ldy", C.c_int64),
+                ("gate", C.c_void_p), ("ldg", C.c_int64), ("gate_bias", C.c_void_p),
+                ("post_norm", C.c_int), ("post_gain", C.c_float), ("replace", C.c_int), ("row_add", C.c_void_p),
+                ("gain", C.c_float), ("eps", C.c_float), ("out", C.c_void_p), ("ldo", C.c_int64),
+                ("concat", C.c_int), ("cat", C.c_void_p), ("dtype", C.c_int), ("rows", C.c_int64), ("D", C.c_int), ("gather", C.c_void_p)]
+
+
+class MinGruParams(C.Structure):
+    _fields_ = [("z", C.c_void_p), ("u", C.c_void_p), ("g", C.c_void_p), ("ld", C.c_int64),
+                ("z_bias", C.c_void_p), ("u_bias", C.c_void_p), ("state", C.c_void_p), ("zero_start", C.c_int),
+                ("out", C.c_void_p), ("ldo", C.c_int64), ("dtype", C.c_int), ("B", C.c_int), ("L", C.c_int64), ("W", C.c_int)]
+
+
+class LatentPrepParams(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("ldq", C.c_int64), ("dkv", C.c_void_p), ("ld_dkv", C.c_int64),
+                ("norm_w", C.c_void_p), ("eps", C.c_float), ("freq", C.c_void_p),
+                ("cache", C.c_void_p), ("cache_row", C.c_int64), ("cache_batch_stride", C.c_int64), ("rank_pad", C.c_int),
+                ("B", C.c_int), ("L", C.c_int64), ("H", C.c_int), ("dim", C.c_int), ("rot", C.c_int), ("rank", C.c_int),
+                ("pos0", C.c_int64), ("pos_dev", C.c_void_p), ("dtype", C.c_int), ("rot_dims", C.c_int)]
+
+
+class LatentDecodeParams(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("ldq", C.c_int64),
+                ("cache", C.c_void_p), ("cache_row", C.c_int64), ("cache_batch_stride", C.c_int64), ("rank_pad", C.c_int),
+                ("uk", C.c_void_p), ("uv", C.c_void_p), ("gate", C.c_void_p), ("ld_gate", C.c_int64),
+                ("out", C.c_void_p), ("ldo", C.c_int64),
+                ("B", C.c_int), ("Lq", C.c_int64), ("H", C.c_int), ("dim", C.c_int), ("rot", C.c_int), ("rank", C.c_int), ("vdim", C.c_int),
+                ("pos0", C.c_int64), ("pos_dev", C.c_void_p), ("window", C.c_int64), ("scale", C.c_float), ("dtype", C.c_int)]
 
 
 # name -> (restype, argtypes); every symbol include/evo_b200.h declares
@@ -144,6 +175,16 @@ SIGNATURES = {
     "evo_hgrn2_fwd": (C.c_int, [C.POINTER(Hgrn2Params), C.c_void_p, C.c_size_t, C.c_void_p]),
     "evo_window_attn_fwd": (C.c_int, [C.POINTER(WindowAttnParams), C.c_void_p]),
     "evo_gemm_simt": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
+    "evo_embed_pair_f32": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_float,
+                                     C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
+    "evo_branch_norm": (C.c_int, [C.POINTER(BranchNormParams), C.c_void_p]),
+    "evo_glu_act": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "evo_scale_logits": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_int, C.c_void_p]),
+    "evo_mingru_workspace": (C.c_size_t, [C.POINTER(MinGruParams)]),
+    "evo_mingru_fwd": (C.c_int, [C.POINTER(MinGruParams), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "evo_latent_prep": (C.c_int, [C.POINTER(LatentPrepParams), C.c_void_p]),
+    "evo_latent_attn_decode": (C.c_int, [C.POINTER(LatentDecodeParams), C.c_void_p]),
+    "evo_moe_route": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]),
 }
 
 _lib = None

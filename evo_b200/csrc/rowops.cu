@@ -223,12 +223,12 @@ __global__ void __launch_bounds__(256) polynorm_kernel(const T* __restrict__ z, 
 }
 
 template <typename T>
-__global__ void softcap_kernel(const T* __restrict__ in, int64_t ldi, float* __restrict__ out, int64_t rows, int V, float cap) {
+__global__ void softcap_kernel(const T* __restrict__ in, int64_t ldi, float* __restrict__ out, int64_t rows, int V, float cap, float mul) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= rows * V) return;
   const int64_t r = i / V; const int c = (int)(i % V);
   const float v = ldf(in + r * ldi + c);
-  out[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+  out[i] = mul * (cap > 0.f ? cap * tanhf(v / cap) : v);
 }
 
 // rows of `width` elements from src (row stride lds) to dst rows [pos, pos + L) of each sequence (row stride ldd, batch stride)
@@ -309,8 +309,8 @@ extern "C" int evo_softcap_logits(const void* in, int64_t ldi, float* out, int64
   if (rows == 0) return 0;
   const int64_t n = rows * V;
   dim3 grid((unsigned)((n + 255) / 256)), block(256);
-  if (dtype) softcap_kernel<float><<<grid, block, 0, (cudaStream_t)stream>>>((const float*)in, ldi, out, rows, V, cap);
-  else softcap_kernel<bf16><<<grid, block, 0, (cudaStream_t)stream>>>((const bf16*)in, ldi, out, rows, V, cap);
+  if (dtype) softcap_kernel<float><<<grid, block, 0, (cudaStream_t)stream>>>((const float*)in, ldi, out, rows, V, cap, 1.f);
+  else softcap_kernel<bf16><<<grid, block, 0, (cudaStream_t)stream>>>((const bf16*)in, ldi, out, rows, V, cap, 1.f);
   return check_launch("evo_softcap_logits");
 }
 
@@ -322,4 +322,158 @@ extern "C" int evo_copy_rows(const void* src, int64_t lds, void* dst, int64_t ld
   if (dtype) copy_rows_kernel<float><<<grid, block, 0, (cudaStream_t)stream>>>((const float*)src, lds, (float*)dst, ldd, dst_batch_stride, B, L, width, pos0, (const long long*)pos_dev);
   else copy_rows_kernel<bf16><<<grid, block, 0, (cudaStream_t)stream>>>((const bf16*)src, lds, (bf16*)dst, ldd, dst_batch_stride, B, L, width, pos0, (const long long*)pos_dev);
   return check_launch("evo_copy_rows");
+}
+
+// =====================================================================================================================
+// Row kernels of the designs whose branches are normed on both sides and gated (Movalorn): token + hashed-pair embedding,
+// the branch close / open kernel, the gated-linear-unit activation with an optional per-row weight per column group, and the
+// final logit scaling.
+namespace {
+
+// out[row] = table[id] * scale + pair[(prev * mul_prev + id * mul_cur) mod buckets], pair row `buckets` when the sequence has no
+// previous token (prev < 0).  prev of a sequence's first new token comes from prev_state[b]; the CTA of that token then stores the
+// sequence's last new token there (it is the only CTA that touches prev_state[b]).
+template <typename IdT>
+__global__ void embed_pair_kernel(const IdT* __restrict__ ids, const bf16* __restrict__ table, const bf16* __restrict__ pair, float* __restrict__ out,
+                                  long long* __restrict__ prev_state, int64_t L, int D, int vocab, float scale,
+                                  long long buckets, long long mul_prev, long long mul_cur) {
+  const int64_t row = blockIdx.x, b = row / L, t = row % L;
+  auto clampid = [vocab](long long v) { return v < 0 ? 0LL : (v >= vocab ? (long long)vocab - 1 : v); };
+  const long long id = clampid((long long)ids[row]);
+  long long prev;
+  if (t > 0) prev = clampid((long long)ids[row - 1]);
+  else prev = prev_state ? prev_state[b] : -1;
+  __syncthreads();
+  if (t == 0 && prev_state && threadIdx.x == 0) prev_state[b] = clampid((long long)ids[b * L + L - 1]);
+  const long long slot = prev < 0 ? buckets : (prev * mul_prev + id * mul_cur) % buckets;
+  const bf16* src = table + (int64_t)id * D;
+  const bf16* pr = pair + (int64_t)slot * D;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) out[row * D + c] = fmaf(__bfloat162float(src[c]), scale, __bfloat162float(pr[c]));
+}
+
+template <typename T>
+__device__ __forceinline__ float gated_value(const T* yr, const T* gr, const bf16* gb, int c) {
+  float u = ldf(yr + c);
+  if (gr) u *= 1.f / (1.f + expf(-(ldf(gr + c) + (gb ? __bfloat162float(gb[c]) : 0.f))));
+  return u;
+}
+
+// One CTA per row:  u = y * sigmoid(gate + gate_bias);  u <- u / rms(u) * post_gain (post_norm);  x <- x + u  (or u + row_add when
+// replace);  then out = x / rms(x) * gain, or (concat) out = [x | cat_row] cast without a norm.  All sums fp32.
+template <typename T>
+__global__ void __launch_bounds__(256) branch_norm_kernel(evo_branch_norm_params p) {
+  __shared__ float red[32];
+  const int64_t r = blockIdx.x;
+  const int64_t srow = p.gather ? p.gather[r] : r;
+  const int D = p.D;
+  float* xr = p.x + srow * D;
+  const T* yr = p.y ? (const T*)p.y + srow * p.ldy : nullptr;
+  const T* gr = (p.y && p.gate) ? (const T*)p.gate + srow * p.ldg : nullptr;
+  const bf16* gb = (const bf16*)p.gate_bias;
+  const bf16* ra = (const bf16*)p.row_add;
+  const bool write_back = p.gather == nullptr && (yr != nullptr || ra != nullptr);
+  float mul = 1.f;
+  if (yr && p.post_norm) {
+    float su = 0.f;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) { const float u = gated_value(yr, gr, gb, c); su = fmaf(u, u, su); }
+    su = block_sum(su, red);
+    mul = p.post_gain / sqrtf(su / (float)D + p.eps);
+  }
+  auto value = [&](int c) {
+    float v = p.replace ? 0.f : xr[c];
+    if (yr) v = fmaf(gated_value(yr, gr, gb, c), mul, v);
+    if (ra) v += __bfloat162float(ra[c]);
+    return v;
+  };
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    const float v = value(c);
+    if (write_back) xr[c] = v;
+    ss = fmaf(v, v, ss);
+  }
+  if (!p.out) return;
+  T* orow = (T*)p.out + r * p.ldo;
+  if (p.concat) {                           // a thread reads back only elements it wrote itself
+    const float* cr = p.cat + srow * D;
+    for (int c = threadIdx.x; c < p.ldo; c += blockDim.x) stf(orow + c, c < D ? (write_back ? xr[c] : value(c)) : (c < 2 * D ? cr[c - D] : 0.f));
+    return;
+  }
+  ss = block_sum(ss, red);
+  const float g = p.gain / sqrtf(ss / (float)D + p.eps);
+  for (int c = threadIdx.x; c < p.ldo; c += blockDim.x) stf(orow + c, c < D ? (write_back ? xr[c] : value(c)) * g : 0.f);
+}
+
+__device__ __forceinline__ float act_value(float z, int act) {
+  if (act == 0) {                         // tanh form of gelu
+    const float t = tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z));
+    return 0.5f * z * (1.f + t);
+  }
+  return z / (1.f + expf(-z));             // silu
+}
+
+// out[r, c] = act(g[r, c]) * u[r, c] * w(r, c) for c < F, zero for F <= c < ldo;  w = group_w[r, c / group] for c < n_groups * group, else 1
+template <typename T>
+__global__ void __launch_bounds__(256) glu_act_kernel(const T* __restrict__ g, const T* __restrict__ u, int64_t ld, T* __restrict__ out, int64_t ldo,
+                                                      int F, int act, const float* __restrict__ group_w, int group, int n_groups) {
+  const int64_t r = blockIdx.x;
+  const T* gr = g + r * ld; const T* ur = u + r * ld;
+  T* orow = out + r * ldo;
+  const float* wr = group_w ? group_w + r * n_groups : nullptr;
+  for (int c = threadIdx.x; c < ldo; c += blockDim.x) {
+    float v = 0.f;
+    if (c < F) {
+      float wt = 1.f;
+      if (wr) { const int e = c / group; if (e < n_groups) wt = wr[e]; }
+      v = wt == 0.f ? 0.f : act_value(ldf(gr + c), act) * ldf(ur + c) * wt;
+    }
+    stf(orow + c, v);
+  }
+}
+
+}  // namespace
+
+extern "C" int evo_embed_pair_f32(const void* ids, int ids_are_i64, const void* table, const void* pair, float* out, int64_t* prev_state,
+                                  int B, int64_t L, int D, int vocab, float scale, int64_t buckets, int64_t mul_prev, int64_t mul_cur, void* stream) {
+  EVO_REQUIRE(ids && table && pair && out && D > 0 && vocab > 0 && buckets > 0, "evo_embed_pair_f32: bad arguments");
+  if ((int64_t)B * L == 0) return 0;
+  dim3 grid((unsigned)((int64_t)B * L)), block(128);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (ids_are_i64) embed_pair_kernel<long long><<<grid, block, 0, st>>>((const long long*)ids, (const bf16*)table, (const bf16*)pair, out, (long long*)prev_state, L, D, vocab, scale, buckets, mul_prev, mul_cur);
+  else embed_pair_kernel<int><<<grid, block, 0, st>>>((const int*)ids, (const bf16*)table, (const bf16*)pair, out, (long long*)prev_state, L, D, vocab, scale, buckets, mul_prev, mul_cur);
+  return check_launch("evo_embed_pair_f32");
+}
+
+extern "C" int evo_branch_norm(const evo_branch_norm_params* p, void* stream) {
+  EVO_REQUIRE(p->x && p->D > 0 && p->rows >= 0, "evo_branch_norm: bad arguments");
+  EVO_REQUIRE(p->out == nullptr || p->ldo >= (p->concat ? 2 * p->D : p->D), "evo_branch_norm: ldo too small");
+  EVO_REQUIRE(p->y == nullptr || p->ldy >= p->D, "evo_branch_norm: ldy < D");
+  EVO_REQUIRE(!p->concat || p->cat, "evo_branch_norm: concat without a second stream");
+  EVO_REQUIRE(!p->replace || p->y, "evo_branch_norm: replace without a branch output");
+  if (p->rows == 0) return 0;
+  dim3 grid((unsigned)p->rows), block(p->D >= 1024 ? 256 : 128);
+  if (p->dtype) branch_norm_kernel<float><<<grid, block, 0, (cudaStream_t)stream>>>(*p);
+  else branch_norm_kernel<bf16><<<grid, block, 0, (cudaStream_t)stream>>>(*p);
+  return check_launch("evo_branch_norm");
+}
+
+extern "C" int evo_glu_act(const void* gate, const void* up, int64_t ld, void* out, int64_t ldo, int64_t rows, int F, int act,
+                           const float* group_w, int group, int n_groups, int dtype, void* stream) {
+  EVO_REQUIRE(gate && up && out && F > 0 && ldo >= F && (act == 0 || act == 1), "evo_glu_act: bad arguments");
+  EVO_REQUIRE(group_w == nullptr || (group > 0 && n_groups > 0), "evo_glu_act: bad groups");
+  if (rows == 0) return 0;
+  dim3 grid((unsigned)rows), block(256);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype) glu_act_kernel<float><<<grid, block, 0, st>>>((const float*)gate, (const float*)up, ld, (float*)out, ldo, F, act, group_w, group, n_groups);
+  else glu_act_kernel<bf16><<<grid, block, 0, st>>>((const bf16*)gate, (const bf16*)up, ld, (bf16*)out, ldo, F, act, group_w, group, n_groups);
+  return check_launch("evo_glu_act");
+}
+
+extern "C" int evo_scale_logits(const void* in, int64_t ldi, float* out, int64_t rows, int V, float mul, int dtype, void* stream) {
+  EVO_REQUIRE(in && out && V > 0 && ldi >= V, "evo_scale_logits: bad arguments");
+  if (rows == 0) return 0;
+  const int64_t n = rows * V;
+  dim3 grid((unsigned)((n + 255) / 256)), block(256);
+  if (dtype) softcap_kernel<float><<<grid, block, 0, (cudaStream_t)stream>>>((const float*)in, ldi, out, rows, V, 0.f, mul);
+  else softcap_kernel<bf16><<<grid, block, 0, (cudaStream_t)stream>>>((const bf16*)in, ldi, out, rows, V, 0.f, mul);
+  return check_launch("evo_scale_logits");
 }

@@ -117,7 +117,8 @@ __device__ __forceinline__ void finish_row(const evo_window_attn_params& p, cons
   float mul = 1.f;
   if (p.head_norm) mul = p.out_scale / sqrtf(warp_sum(ss) / (float)dv + p.norm_eps);
   T* orow = (T*)p.out + row * p.ldo;
-  const T* grow = p.gate ? (const T*)p.gate + row * p.gate_tok_stride + h * dv : nullptr;
+  const T* grow = (p.gate && !p.gate_per_head) ? (const T*)p.gate + row * p.gate_tok_stride + h * dv : nullptr;
+  if (p.gate && p.gate_per_head) mul *= 1.f / (1.f + expf(-ldf((const T*)p.gate + row * p.gate_tok_stride + h)));
 #pragma unroll
   for (int c = 0; c < MAXCV; ++c) {
     const int ch = BLOCKED ? lane * MAXCV + c : lane + 32 * c;

@@ -265,8 +265,9 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
     if (rel >= p.Lq) continue;
     const int64_t row = (int64_t)b * p.Lq + rel;
     bf16* orow = (bf16*)p.out + row * p.ldo + (int64_t)h * dv;
-    const bf16* grow = p.gate ? (const bf16*)p.gate + row * p.gate_tok_stride + (int64_t)h * dv : nullptr;
-    const float mul = r == 0 ? mul0 : mul1;
+    const bf16* grow = (p.gate && !p.gate_per_head) ? (const bf16*)p.gate + row * p.gate_tok_stride + (int64_t)h * dv : nullptr;
+    float mul = r == 0 ? mul0 : mul1;
+    if (p.gate && p.gate_per_head) mul *= 1.f / (1.f + expf(-__bfloat162float(((const bf16*)p.gate)[row * p.gate_tok_stride + h])));
 #pragma unroll
     for (int n = 0; n < NV8; ++n) {
       const int ch = n * 8 + qc;

@@ -97,10 +97,11 @@ def load_checkpoint(model_name: str = "evo-1-8k-base", config_path: Optional[str
     return model
 
 
-def _load_zaverax(model_dir: str, config: dict, device, dtype, **kwargs):
+def _load_flat(family, model_dir: str, config: dict, device, dtype):
+    """Families described by a flat table of checkpoint tensors (StreamDecoder subclasses)."""
     from .ingest import load_named_tensors
-    from .zaverax import Zaverax, ZaveraxConfig
-    model = Zaverax(ZaveraxConfig.from_dict(config), dtype=dtype or torch.bfloat16)
+    cls, cfg_cls = family()
+    model = cls(cfg_cls.from_dict(config), dtype=dtype or torch.bfloat16)
     dev = torch.device(device) if device is not None else torch.device("cpu")
     shapes = {k: tuple(v.shape) for k, v in model.weights.items()}
     tensors, model.ingest_stats = load_named_tensors(model_dir, dev, shapes, type(model).__name__)
@@ -108,6 +109,20 @@ def _load_zaverax(model_dir: str, config: dict, device, dtype, **kwargs):
         model.weights[name] = t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16)
     model._invalidate()
     return model
+
+
+def _load_zaverax(model_dir: str, config: dict, device, dtype, **kwargs):
+    def family():
+        from .zaverax import Zaverax, ZaveraxConfig
+        return Zaverax, ZaveraxConfig
+    return _load_flat(family, model_dir, config, device, dtype)
+
+
+def _load_movalorn(model_dir: str, config: dict, device, dtype, **kwargs):
+    def family():
+        from .movalorn import Movalorn, MovalornConfig
+        return Movalorn, MovalornConfig
+    return _load_flat(family, model_dir, config, device, dtype)
 
 
 def _load_stripedhyena(model_dir: str, config: dict, device, dtype, model_name: str = "evo-1-8k-base", **kwargs):
@@ -119,6 +134,7 @@ def _load_stripedhyena(model_dir: str, config: dict, device, dtype, model_name: 
 # config.json "architecture" -> (loader, activation dtypes the model class can run in)
 ARCHITECTURES = {
     "Zaverax": (_load_zaverax, (torch.bfloat16, torch.float32)),
+    "Movalorn": (_load_movalorn, (torch.bfloat16, torch.float32)),
     "StripedHyena": (_load_stripedhyena, (torch.bfloat16,)),
     "StripedHyenaModelForCausalLM": (_load_stripedhyena, (torch.bfloat16,)),
 }

@@ -353,12 +353,101 @@ typedef struct {
   int64_t window, keep_first;
   float scale, lambda;
   int head_norm; float norm_eps, out_scale;
+  int gate_per_head;      /* 1: gate holds one number per head (column h), else one per output channel (column h*dv + c) */
 } evo_window_attn_params;
 int evo_window_attn_fwd(const evo_window_attn_params* p, void* stream);
 
 /* C (M, N) = A (M, K) . W (N, K)^T with fp32 multiply-add on the CUDA cores (no tensor-core rounding): the linear layer of the
  * all-fp32 mode, and a shape-agnostic comparator for the bf16 one.  A and C have `dtype`; W is bf16. */
 int evo_gemm_simt(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K, int dtype, void* stream);
+
+/* ==== designs whose branches are gated and normed on both sides, with latent attention, a minimal gated recurrence and
+ * expert mixtures (Movalorn).  Same conventions: `dtype` 0 = bf16 activations, 1 = fp32; weights and parameter vectors bf16. ==== */
+
+/* out (B*L, D) fp32 = table[id] * scale + pair[(prev * mul_prev + id * mul_cur) mod buckets]; a sequence without a previous token
+ * uses pair row `buckets`.  prev_state (B) int64 (optional): the token before this call's first one (-1: none); the call leaves the
+ * sequence's last token there. */
+int evo_embed_pair_f32(const void* ids, int ids_are_i64, const void* table, const void* pair, float* out, int64_t* prev_state,
+                       int B, int64_t L, int D, int vocab, float scale, int64_t buckets, int64_t mul_prev, int64_t mul_cur, void* stream);
+
+/* Closes one branch and opens the next, one pass per row of the fp32 stream x (rows, D):
+ *   u = y * sigmoid(gate + gate_bias)          (gate NULL: u = y)
+ *   u = u / sqrt(mean(u^2) + eps) * post_gain   (post_norm)
+ *   x <- x + u + row_add                        (replace: x <- u + row_add; y NULL: x unchanged)
+ *   out = x / sqrt(mean(x^2) + eps) * gain      (concat: out = [x | cat] cast, no norm; out NULL: nothing)
+ * gather (rows) int64: row i of out comes from stream row gather[i] and x is not written back.  Pad columns of out are zero. */
+typedef struct {
+  float* x;
+  const void* y; int64_t ldy;
+  const void* gate; int64_t ldg; const void* gate_bias;
+  int post_norm; float post_gain;
+  int replace; const void* row_add;
+  float gain, eps;
+  void* out; int64_t ldo;
+  int concat; const float* cat;
+  int dtype;
+  int64_t rows; int D;
+  const int64_t* gather;
+} evo_branch_norm_params;
+int evo_branch_norm(const evo_branch_norm_params* p, void* stream);
+
+/* out[r, c] = act(gate[r, c]) * up[r, c] * w,  act 0 = tanh-form gelu, 1 = silu;  w = group_w[r, c / group] for c < n_groups * group
+ * (fp32, rows x n_groups; NULL: 1) -- the weights of an expert mixture computed densely; columns [F, ldo) are zero. */
+int evo_glu_act(const void* gate, const void* up, int64_t ld, void* out, int64_t ldo, int64_t rows, int F, int act,
+                const float* group_w, int group, int n_groups, int dtype, void* stream);
+/* out (rows, V) fp32 = in * mul */
+int evo_scale_logits(const void* in, int64_t ldi, float* out, int64_t rows, int V, float mul, int dtype, void* stream);
+
+/* minGRU: per channel, with the raw projections z, u, g of a row (one fused buffer, row stride ld),
+ *   a = sigmoid(z + z_bias), c = u + u_bias, cand = c + 1/2 (c >= 0) | sigmoid(c) (c < 0),  S <- (1 - a) S + a cand,  out = S * silu(g).
+ * S (B, W) fp32 is read (unless zero_start) and written back (unless NULL); gates, candidate and state are fp32.
+ * Long sequences are scanned in chunks (chunk products first, then each chunk from its carried-in state):
+ * workspace evo_mingru_workspace() bytes. */
+typedef struct {
+  const void* z; const void* u; const void* g; int64_t ld;
+  const void* z_bias; const void* u_bias;
+  float* state; int zero_start;
+  void* out; int64_t ldo; int dtype;
+  int B; int64_t L; int W;
+} evo_mingru_params;
+size_t evo_mingru_workspace(const evo_mingru_params* p);
+int evo_mingru_fwd(const evo_mingru_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Latent attention, preparation of a row of projections: the rotated part of every query head is turned in place, the first
+ * `rank` entries of the down projection are RMS-normed (weight `norm_w`) into the latent, its last `rot` entries are turned, and
+ * [latent | zeros up to rank_pad | rotated key part] is written to the cache row of the token's position
+ * (pos = *pos_dev if given else pos0, plus the token's index).  Pairs (2i, 2i+1), 2i < rot_dims, turn by pos * freq[i] (freq fp32, rot_dims/2 entries). */
+typedef struct {
+  void* q; int64_t ldq;                       /* (B*L, H*(dim+rot)) in place */
+  const void* dkv; int64_t ld_dkv;            /* (B*L, rank+rot) */
+  const void* norm_w; float eps;
+  const float* freq;
+  void* cache; int64_t cache_row, cache_batch_stride; int rank_pad;
+  int B; int64_t L; int H, dim, rot, rank;
+  int64_t pos0; const int64_t* pos_dev; int dtype;
+  int rot_dims;                               /* leading entries of a rotated part that are turned (even, <= rot) */
+} evo_latent_prep_params;
+int evo_latent_prep(const evo_latent_prep_params* p, void* stream);
+
+/* Latent attention for few query rows (the decoding step) straight from the latent cache, in the absorbed form:
+ *   ql = Uk_h^T q_a (rank),  s_j = (ql . c_j + q_b . kr_j) * scale over the visible j,  w = softmax(s),
+ *   o = Uv_h (sum_j w_j c_j),  out_h = o * sigmoid(gate_h);   key j is visible from i iff 0 <= i - j < window (window <= 0: j <= i).
+ * Everything between the bf16 (or fp32) inputs and the output is fp32. */
+typedef struct {
+  const void* q; int64_t ldq;                 /* prepared queries (B*Lq, H*(dim+rot)) */
+  const void* cache; int64_t cache_row, cache_batch_stride; int rank_pad;
+  const void* uk; const void* uv;             /* (H*dim, rank), (H*vdim, rank) bf16 */
+  const void* gate; int64_t ld_gate;          /* (B*Lq, H) raw, optional */
+  void* out; int64_t ldo;
+  int B; int64_t Lq; int H, dim, rot, rank, vdim;
+  int64_t pos0; const int64_t* pos_dev; int64_t window; float scale; int dtype;
+} evo_latent_decode_params;
+int evo_latent_attn_decode(const evo_latent_decode_params* p, void* stream);
+
+/* Expert router: logits = W (E, D) . h in fp32, s = softmax(logits), the `top` experts with the largest s + correction are chosen;
+ * weights (rows, E) fp32 = s * scale for the chosen experts, 0 for the others; chosen (rows, top) int32 (optional). */
+int evo_moe_route(const void* h, int64_t ldh, const void* router_w, const void* correction, float* weights, int32_t* chosen,
+                  int64_t rows, int D, int E, int top, float scale, int dtype, void* stream);
 
 #ifdef __cplusplus
 }
