@@ -22,7 +22,7 @@ def _write_checkpoint(folder, cfg, tensors):
         json.dump(cfg, f)
     header, blobs, off = {}, [], 0
     for name, t in tensors.items():
-        raw = t.contiguous().view(torch.uint8).numpy().tobytes()
+        raw = t.contiguous().reshape(-1).view(torch.uint8).numpy().tobytes()          # reshape: 0-dim tensors too
         header[name] = {"dtype": {torch.bfloat16: "BF16", torch.float32: "F32"}[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
         blobs.append(raw)
         off += len(raw)
