@@ -69,11 +69,19 @@ def test_branch_norm_modes(D, ldo):
     lib = _lib.lib()
     u = y[:, :D].double() * torch.sigmoid(gate[:, :D].double() + gb.double())
     # gated, normed branch added to the stream, then the next norm
-    xd, out = x.to(DEV), torch.full((M, ldo), 7.0, device=DEV)
-    p = BranchNormParams(x=xd.data_ptr(), y=yd.data_ptr(), ldy=D + 8, gate=gd.data_ptr(), ldg=D + 16, gate_bias=gbd.data_ptr(), post_norm=1, post_gain=0.7,
-                         gain=1.3, eps=eps, out=out.data_ptr(), ldo=ldo, dtype=0, rows=M, D=D)
-    check(lib.evo_branch_norm(C.byref(p), _stream()))
     xn = x.double() + O.scalar_norm(u, 0.7, eps)
+    xb, outb = x.to(DEV), torch.full((M, ldo), 7.0, dtype=B16, device=DEV)                 # bf16 activations in and out
+    pb = BranchNormParams(x=xb.data_ptr(), y=yd.data_ptr(), ldy=D + 8, gate=gd.data_ptr(), ldg=D + 16, gate_bias=gbd.data_ptr(), post_norm=1, post_gain=0.7,
+                          gain=1.3, eps=eps, out=outb.data_ptr(), ldo=ldo, dtype=0, rows=M, D=D)
+    check(lib.evo_branch_norm(C.byref(pb), _stream()))
+    _close(xb, xn, 1e-6, "stream, bf16 branch")
+    _close(outb[:, :D], O.scalar_norm(xn, 1.3, eps), 5e-3, "opened norm in bf16")
+    assert (outb[:, D:] == 0).all()
+    yf, gf = y.float().to(DEV), gate.float().to(DEV)
+    xd, out = x.to(DEV), torch.full((M, ldo), 7.0, device=DEV)
+    p = BranchNormParams(x=xd.data_ptr(), y=yf.data_ptr(), ldy=D + 8, gate=gf.data_ptr(), ldg=D + 16, gate_bias=gbd.data_ptr(), post_norm=1, post_gain=0.7,
+                         gain=1.3, eps=eps, out=out.data_ptr(), ldo=ldo, dtype=1, rows=M, D=D)
+    check(lib.evo_branch_norm(C.byref(p), _stream()))
     _close(xd, xn, 1e-6, "stream")
     _close(out[:, :D], O.scalar_norm(xn, 1.3, eps), 1e-6, "opened norm")
     assert (out[:, D:] == 0).all()
@@ -86,7 +94,6 @@ def test_branch_norm_modes(D, ldo):
     assert torch.equal(xd2.cpu(), x)
     # replace: the stream becomes the branch plus a row vector; fp32 activations
     xd3, out3 = x.to(DEV), torch.full((M, ldo), 7.0, device=DEV)
-    yf = y.float().to(DEV)
     p3 = BranchNormParams(x=xd3.data_ptr(), y=yf.data_ptr(), ldy=D + 8, replace=1, row_add=sd.data_ptr(), gain=0.9, eps=eps, out=out3.data_ptr(), ldo=ldo,
                           dtype=1, rows=M, D=D)
     check(lib.evo_branch_norm(C.byref(p3), _stream()))
