@@ -1,6 +1,6 @@
 """bench.py — nucleotides/sec of the Evo-1 7B forward on B200 (BASELINE.json metric).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload 8k|131k|1k|32k|gen|zaverax] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload 8k|131k|1k|32k|gen|zaverax|movalorn] [--impl ours|reference]
 
 Workload "8k" (default, BASELINE.json configs[1]): evo-1-8k-base scoring forward, batch 8 x
 8192 nt of synthetic uniform ACGT (+BOS => L = 8193), bf16, random-init weights of the 7B
@@ -11,7 +11,8 @@ architecture (no network for checkpoints).  One "step" = one forward over one ba
 N > 1 (torchrun, one rank per GPU): independent replicas of the workload, no data-path
 collective (weak scaling); "131k" runs the sequence-parallel forward instead.
 Workload "zaverax" (an option; the default workload and its JSON contract are unchanged): the Zaverax design beside StripedHyena at
-equal layer sizes, prefill and decode, with a per-kernel roofline breakdown (bench_arch).
+equal layer sizes, prefill and decode, with a per-kernel roofline breakdown (bench_arch).  Workload "movalorn": the same for the
+Movalorn design beside Zaverax, the closest family.
 --impl reference: the reference's own CPU implementation of the path.  stripedhyena==0.2.2 is
 not installable offline, so this arm times the oracle restatement (kind "port") on the host
 cores, rank 0 only, on a bounded sample of the same workload.
@@ -601,6 +602,34 @@ def _arch_models(size, dev):
     return zv, sh
 
 
+def _movalorn_models(size, dev):
+    """A Movalorn model and a Zaverax model (the closest family: fp32 stream, recurrent layers plus one windowed-attention layer) of
+    equal width, depth, head count, window and feed-forward width, random weights.  Movalorn: latent 512 + 64 rotated, heads of
+    64 + 64 query and 128 value channels; two dense feed-forwards and two with 16 experts (4 chosen, one shared) whose chosen hidden
+    width equals the dense one."""
+    from evo_b200.movalorn import Movalorn, MovalornConfig
+    from evo_b200.zaverax import Zaverax, ZaveraxConfig
+    s = ARCH_SIZES[size]
+    d, H = s["width"], s["heads"]
+    ff = (8 * d // 3 + 255) // 256 * 256
+    rec = {"type": "hgrn2", "mixer": {"heads": H, "dim": 128, "vdim": 128}, "mlp": {"kind": "dense", "ff": ff}}
+    att = {"type": "attention", "mixer": {"heads": H, "kv_heads": H, "dim": 64, "vdim": 128, "scale": 0.125, "diff": 0.5, "mask": {"size": 1024, "keep_first": 0}},
+           "mlp": {"kind": "dense", "ff": ff}}
+    zc = {"architecture": "Zaverax", "vocab": 512, "width": d, "layers": [rec, att, rec, rec], "norm": {"eps": 1e-5}, "canon": {"taps": 3},
+          "loop": {"start": 0, "stop": 0, "times": 1}, "residual_mult": 0.5, "logit_softcap": 15.0}
+    zv = Zaverax(ZaveraxConfig.from_dict(zc)).init_random(0, device=dev)
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": 16, "top": 4, "scale": 1.0}, "shared": {"ff": ff // 4}}
+    gru = {"type": "mingru", "mixer": {"width": d}}
+    lat = {"type": "latent_attention", "mixer": {"heads": H, "dim": 64, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 1.0 / 128 ** 0.5,
+                                                 "mask": {"size": 1024}, "rot": {"base": 10000.0, "dims": 64}}}
+    mc = {"architecture": "Movalorn", "vocab": 512, "width": d, "norm": {"eps": 1e-5}, "logit_scale": 1.0,
+          "embedding": {"scale": 1.0, "bigram": {"buckets": 4093, "mul_prev": 31, "mul_cur": 7}},
+          "layers": [dict(gru, mlp=dense), dict(lat, mlp=moe), dict(gru, mlp=moe), dict(gru, mlp=dense)]}
+    mv = Movalorn(MovalornConfig.from_dict(mc)).init_random(0, device=dev)
+    return mv, zv
+
+
 def bench_arch(args):
     """--workload zaverax: prefill and decode throughput of the Zaverax design beside StripedHyena at equal layer sizes (random
     weights, 4 layers each, one of them attention), with a per-kernel breakdown against the measured rooflines.  Inputs are larger
@@ -614,14 +643,17 @@ def bench_arch(args):
     fp32_lane_ops = 148 * 128 * peaks.get("sm_max_mhz", 1965.0) * 1e6        # CUDA-core fp32 instructions (lanes) per second at the maximum clock
     bound = {"gemm": ("flop/s", peaks["bf16_tflops"] * 1e12), "gemm_simt": ("flop/s", 2 * fp32_lane_ops), "attn": ("flop/s", peaks["bf16_tflops"] * 1e12),
              "window_attn": ("flop/s", peaks["bf16_tflops"] * 1e12), "hgrn2": ("fp32 lane-op/s", fp32_lane_ops)}
-    out = {"workload": "zaverax", "metric": "tokens/sec, prefill and decode, Zaverax beside StripedHyena at equal sizes", "unit": "tok/s", "dtype": "bf16",
+    family = args.workload
+    other = {"zaverax": "stripedhyena", "movalorn": "zaverax"}[family]
+    bound.update({"mingru": ("B/s", peaks["hbm_gbs"] * 1e9), "latent_decode": ("B/s", peaks["hbm_gbs"] * 1e9)})
+    out = {"workload": family, "metric": f"tokens/sec, prefill and decode, {family} beside {other} at equal sizes", "unit": "tok/s", "dtype": "bf16",
            "data": "synthetic", "steps": steps, "warmup": warmup, "peaks": peaks, "sizes": {}}
     launches = 0
     with ClockSampler(0) as clocks:
         for size, s in ARCH_SIZES.items():
-            zv, sh = _arch_models(size, dev)
+            zv, sh = _arch_models(size, dev) if family == "zaverax" else _movalorn_models(size, dev)
             rec = {}
-            for name, model in (("zaverax", zv), ("stripedhyena", sh)):
+            for name, model in ((family, zv), (other, sh)):
                 B, L = s["prefill"]
                 ids = torch.randint(0, 512, (B, L), device=dev)
                 fwd = lambda: model(ids)
@@ -644,7 +676,7 @@ def bench_arch(args):
                 d["mha"].max_seqlen = ctx + 512
                 lg, d = model(pids, inference_params_dict=d)
                 nsteps = 64
-                if name == "zaverax":
+                if name != "stripedhyena":
                     tok0 = lg[:, -1].argmax(-1)
                     model.decode_loop(tok0, d, 8, ctx, top_k=1)                       # warm-up: eager step + graph capture
                     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -680,7 +712,7 @@ def bench_arch(args):
             out["sizes"][size] = rec
             del zv, sh
             torch.cuda.empty_cache()
-    out["value"] = out["sizes"]["4k"]["zaverax"]["prefill_tok_s"]
+    out["value"] = out["sizes"]["4k"][family]["prefill_tok_s"]
     out["n_gpus"] = 1
     out["gpu_launches"] = int(launches)
     out["higher_is_better"] = True
@@ -694,14 +726,14 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="8k", choices=list(WORKLOADS) + ["zaverax"])
+    ap.add_argument("--workload", default="8k", choices=list(WORKLOADS) + ["zaverax", "movalorn"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sub", action="store_true", help="default workload only: skip the sp131k / gen sub-records")
     ap.add_argument("--no-gen", action="store_true", help="skip the cached-generation sub-record")
     ap.add_argument("--sub-steps", type=int, default=3, help="timed steps of the 131k sub-record")
     ap.add_argument("--gen-tokens", type=int, default=None, help="new tokens of the end-to-end generate() run (default: 4096 = BASELINE configs[3])")
     args = ap.parse_args()
-    if args.workload == "zaverax":
+    if args.workload in ("zaverax", "movalorn"):
         return bench_arch(args)
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":

@@ -126,7 +126,7 @@ class LatentDecodeParams(C.Structure):
                 ("uk", C.c_void_p), ("uv", C.c_void_p), ("gate", C.c_void_p), ("ld_gate", C.c_int64),
                 ("out", C.c_void_p), ("ldo", C.c_int64),
                 ("B", C.c_int), ("Lq", C.c_int64), ("H", C.c_int), ("dim", C.c_int), ("rot", C.c_int), ("rank", C.c_int), ("vdim", C.c_int),
-                ("pos0", C.c_int64), ("pos_dev", C.c_void_p), ("window", C.c_int64), ("scale", C.c_float), ("dtype", C.c_int)]
+                ("pos0", C.c_int64), ("pos_dev", C.c_void_p), ("window", C.c_int64), ("scale", C.c_float), ("dtype", C.c_int), ("max_keys", C.c_int64)]
 
 
 # name -> (restype, argtypes); every symbol include/evo_b200.h declares
@@ -183,7 +183,8 @@ SIGNATURES = {
     "evo_mingru_workspace": (C.c_size_t, [C.POINTER(MinGruParams)]),
     "evo_mingru_fwd": (C.c_int, [C.POINTER(MinGruParams), C.c_void_p, C.c_size_t, C.c_void_p]),
     "evo_latent_prep": (C.c_int, [C.POINTER(LatentPrepParams), C.c_void_p]),
-    "evo_latent_attn_decode": (C.c_int, [C.POINTER(LatentDecodeParams), C.c_void_p]),
+    "evo_latent_attn_decode_workspace": (C.c_size_t, [C.POINTER(LatentDecodeParams)]),
+    "evo_latent_attn_decode": (C.c_int, [C.POINTER(LatentDecodeParams), C.c_void_p, C.c_size_t, C.c_void_p]),
     "evo_moe_route": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]),
 }
 

@@ -3,15 +3,19 @@
 //
 //   evo_latent_prep         one CTA per token: turns the rotated part of every query head in place (interleaved pairs, fp32 angles
 //                           pos * freq[i]), RMS-norms the latent (fp32) and appends [latent | 0.. | turned key part] to the cache.
-//   evo_latent_attn_decode  few query rows (the decoding step, short portions): the absorbed form.  A CTA owns one (query, head):
-//                           ql = Uk_h^T q_a, scores straight against the cached latents (one warp per key, lanes across the latent),
-//                           chunked streaming softmax, the weighted sum of latents, then o = Uv_h . sum -- the window's keys and
-//                           values are never expanded.  Every intermediate is fp32.
+//   evo_latent_attn_decode  few query rows (the decoding step, short portions): the absorbed form, ql = Uk_h^T q_a, scores straight
+//                           against the cached latents, streaming softmax, the weighted sum of latents, then o = Uv_h . sum -- the
+//                           window's keys and values are never expanded, and every intermediate is fp32.  Three launches: absorb
+//                           (Uk read once), a (key split, row, head group) kernel in which 8 or 16 heads share each tile of latents
+//                           through shared memory, and a merge that applies Uv and the head gate.  Shapes that path does not
+//                           cover run one CTA per (query, head) (latent_decode_kernel).
 // Prompts and long portions expand the visible rows of the cache with one GEMM against [Uk ; Uv] (the rotated part is carried into
 // every head's key by identity rows of that weight) and run the windowed attention kernel on the result.
 #include "common.cuh"
 #include "../../include/evo_b200.h"
 #include <math.h>
+#include <stdlib.h>
+#include <algorithm>
 
 using namespace evo;
 
@@ -190,6 +194,181 @@ __global__ void __launch_bounds__(DT) latent_decode_kernel(evo_latent_decode_par
     for (int64_t c = (int64_t)p.H * p.vdim + tid; c < p.ldo; c += DT) stf(orow + c, 0.f);
 }
 
+// ---- few query rows, all heads of a group share every latent they read ------------------------------------------------------------
+// (1) absorb: ql[row, h] = [Uk_h^T q_a | q_b]  (fp32, rank + rot entries).  grid (H, rank / 128); the weights are read once per 8 rows.
+constexpr int AR = 8;         // rows per pass of the absorb kernel
+template <typename T>
+__global__ void __launch_bounds__(128) latent_absorb_kernel(evo_latent_decode_params p, float* __restrict__ ql) {
+  extern __shared__ float qs[];             // [AR][dim]
+  const int h = blockIdx.x, r = blockIdx.y * 128 + threadIdx.x;
+  const int hd = p.dim + p.rot, kw = p.rank + p.rot;
+  const int64_t R = (int64_t)p.B * p.Lq;
+  const bf16* uk = (const bf16*)p.uk + (int64_t)h * p.dim * p.rank;
+  for (int64_t row0 = 0; row0 < R; row0 += AR) {
+    const int nr = (int)min((int64_t)AR, R - row0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nr * p.dim; idx += 128) {
+      const int i = idx / p.dim, d = idx % p.dim;
+      qs[i * p.dim + d] = ldf((const T*)p.q + (row0 + i) * p.ldq + (int64_t)h * hd + d);
+    }
+    if (blockIdx.y == 0)
+      for (int idx = threadIdx.x; idx < nr * p.rot; idx += 128) {
+        const int i = idx / p.rot, e = idx % p.rot;
+        ql[((row0 + i) * p.H + h) * kw + p.rank + e] = ldf((const T*)p.q + (row0 + i) * p.ldq + (int64_t)h * hd + p.dim + e);
+      }
+    __syncthreads();
+    if (r < p.rank) {
+      float acc[AR];
+#pragma unroll
+      for (int i = 0; i < AR; ++i) acc[i] = 0.f;
+      for (int d = 0; d < p.dim; ++d) {
+        const float w = __bfloat162float(uk[(int64_t)d * p.rank + r]);
+#pragma unroll
+        for (int i = 0; i < AR; ++i) acc[i] = fmaf(qs[(i < nr ? i : 0) * p.dim + d], w, acc[i]);
+      }
+      for (int i = 0; i < nr; ++i) ql[((row0 + i) * p.H + h) * kw + r] = acc[i];
+    }
+  }
+}
+
+// (2) scores and value sums of one (key split, row, head group): tiles of KT = 256 / HG latents go through shared memory once for all HG heads;
+// thread (head, key) scores, thread (head, r0) accumulates the latent entries r0 + KT * k.  Partial (max, sum, acc) per split.
+constexpr int SPLIT_T = 256;
+constexpr int RMAX = 32;      // latent entries per thread
+template <typename T, int HG>
+__global__ void __launch_bounds__(SPLIT_T) latent_split_kernel(evo_latent_decode_params p, const float* __restrict__ ql, float* __restrict__ part, int n_split) {
+  constexpr int KT = SPLIT_T / HG;          // keys per tile = threads per head (16 or 32: a head's threads sit in one warp)
+  extern __shared__ float sm[];
+  const int kw = p.rank + p.rot, tw = kw + 1;
+  float* qs = sm;                           // [HG][kw]
+  float* tile = qs + HG * kw;               // [KT][kw + 1]
+  float* pb = tile + KT * tw;               // [HG][KT]
+  const int split = blockIdx.x, hg = blockIdx.z;
+  const int64_t row = blockIdx.y, b = row / p.Lq, rel = row % p.Lq;
+  const int tid = threadIdx.x, hl = tid / KT, kk = tid % KT, w = tid >> 5, lane = tid & 31;
+  const int h = hg * HG + hl;
+  const bool live = h < p.H;
+  const int64_t i = (p.pos_dev ? (int64_t)*p.pos_dev : p.pos0) + rel;
+  const int64_t lo = p.window > 0 ? max((int64_t)0, i - p.window + 1) : 0;
+  const int64_t n = i - lo + 1;
+  const int64_t tiles = (n + KT - 1) / KT, per = (tiles + n_split - 1) / n_split;
+  const int64_t t_begin = split * per, t_end = min(tiles, t_begin + per);
+  for (int idx = tid; idx < HG * kw; idx += SPLIT_T) {
+    const int hh = hg * HG + idx / kw;
+    qs[idx] = hh < p.H ? ql[(row * p.H + hh) * kw + idx % kw] : 0.f;
+  }
+  const T* cb = (const T*)p.cache + b * p.cache_batch_stride;
+  float acc[RMAX];
+#pragma unroll
+  for (int k = 0; k < RMAX; ++k) acc[k] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;
+  for (int64_t t = t_begin; t < t_end; ++t) {
+    const int64_t k0 = lo + t * KT;
+    const int nk = (int)min((int64_t)KT, i + 1 - k0);
+    __syncthreads();
+    for (int key = w; key < nk; key += SPLIT_T / 32) {
+      const T* c = cb + (k0 + key) * p.cache_row;
+      for (int e = lane; e < p.rank; e += 32) tile[key * tw + e] = ldf(c + e);
+      for (int e = lane; e < p.rot; e += 32) tile[key * tw + p.rank + e] = ldf(c + p.rank_pad + e);
+    }
+    __syncthreads();
+    float sc = -INFINITY;
+    if (kk < nk) {
+      float d = 0.f;
+      const float* qv = qs + hl * kw;
+      const float* cv = tile + kk * tw;
+      for (int e = 0; e < kw; ++e) d = fmaf(qv[e], cv[e], d);
+      sc = d * p.scale;
+    }
+    float mx = sc;
+#pragma unroll
+    for (int o = KT / 2; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float m_new = fmaxf(m_run, mx);               // finite: every tile of the range has a visible key
+    const float corr = expf(m_run - m_new);
+    const float pj = kk < nk ? expf(sc - m_new) : 0.f;
+    float ps = pj;
+#pragma unroll
+    for (int o = KT / 2; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+    l_run = l_run * corr + ps;
+    m_run = m_new;
+    pb[hl * KT + kk] = pj;
+    __syncwarp();                                       // a head's KT probabilities are written and read by lanes of one warp
+#pragma unroll
+    for (int k = 0; k < RMAX; ++k) acc[k] *= corr;
+    for (int key = 0; key < nk; ++key) {
+      const float pk = pb[hl * KT + key];
+      const float* cv = tile + key * tw + kk;
+#pragma unroll
+      for (int k = 0; k < RMAX; ++k)
+        if (kk + k * KT < p.rank) acc[k] = fmaf(pk, cv[k * KT], acc[k]);
+    }
+  }
+  if (!live) return;
+  float* dst = part + (((int64_t)split * gridDim.y + row) * p.H + h) * (p.rank + 2);
+  if (kk == 0) { dst[0] = m_run; dst[1] = l_run; }
+#pragma unroll
+  for (int k = 0; k < RMAX; ++k)
+    if (kk + k * KT < p.rank) dst[2 + kk + k * KT] = acc[k];
+}
+
+// (3) merge of the splits, o = Uv_h . (sum / l), head gate, store: one CTA per (row, head)
+template <typename T>
+__global__ void __launch_bounds__(256) latent_merge_kernel(evo_latent_decode_params p, const float* __restrict__ part, int n_split) {
+  extern __shared__ float ol[];             // [rank]
+  const int64_t row = blockIdx.x;
+  const int h = blockIdx.y, tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
+  const int64_t R = gridDim.x, stride = (int64_t)p.rank + 2;
+  float mx = -INFINITY;
+  for (int s = 0; s < n_split; ++s) mx = fmaxf(mx, part[(((int64_t)s * R + row) * p.H + h) * stride]);
+  float l = 0.f;
+  for (int s = 0; s < n_split; ++s) {
+    const float* src = part + (((int64_t)s * R + row) * p.H + h) * stride;
+    if (src[0] != -INFINITY) l = fmaf(src[1], expf(src[0] - mx), l);
+  }
+  const float inv = 1.f / l;
+  for (int r = tid; r < p.rank; r += 256) {
+    float t = 0.f;
+    for (int s = 0; s < n_split; ++s) {
+      const float* src = part + (((int64_t)s * R + row) * p.H + h) * stride;
+      if (src[0] != -INFINITY) t = fmaf(src[2 + r], expf(src[0] - mx), t);
+    }
+    ol[r] = t * inv;
+  }
+  __syncthreads();
+  float gate = 1.f;
+  if (p.gate) gate = 1.f / (1.f + expf(-ldf((const T*)p.gate + row * p.ld_gate + h)));
+  const bf16* uv = (const bf16*)p.uv + (int64_t)h * p.vdim * p.rank;
+  T* orow = (T*)p.out + row * p.ldo;
+  for (int v = w; v < p.vdim; v += 8) {
+    float d = 0.f;
+    for (int r = lane; r < p.rank; r += 32) d = fmaf(__bfloat162float(uv[(int64_t)v * p.rank + r]), ol[r], d);
+    d = warp_sum(d);
+    if (lane == 0) stf(orow + (int64_t)h * p.vdim + v, d * gate);
+  }
+  if (h == p.H - 1)
+    for (int64_t c = (int64_t)p.H * p.vdim + tid; c < p.ldo; c += 256) stf(orow + c, 0.f);
+}
+
+// plan of the shared-heads path: heads per group (0: not covered, the per-head kernel runs) and the number of key splits
+struct SplitPlan { int hg, n_split; size_t smem, ws; };
+inline SplitPlan split_plan(const evo_latent_decode_params* p) {
+  SplitPlan pl = {0, 1, 0, 0};
+  if (p->H >= 12 && p->rank <= 16 * RMAX) pl.hg = 16;
+  else if (p->rank <= 32 * RMAX) pl.hg = 8;
+  else return pl;
+  const int kt = SPLIT_T / pl.hg, kw = p->rank + p->rot;
+  pl.smem = sizeof(float) * ((size_t)pl.hg * kw + (size_t)kt * (kw + 1) + SPLIT_T);
+  if (pl.smem > 200 * 1024) { pl.hg = 0; return pl; }
+  const int64_t R = (int64_t)p->B * p->Lq, groups = (p->H + pl.hg - 1) / pl.hg;
+  const int64_t keys = p->max_keys > 0 ? (p->window > 0 ? std::min<int64_t>(p->window, p->max_keys) : p->max_keys) : (p->window > 0 ? p->window : 1024);
+  const int64_t tiles = (keys + kt - 1) / kt;
+  int64_t s = (2 * 148 + R * groups - 1) / (R * groups);
+  s = std::max<int64_t>(1, std::min<int64_t>(s, (tiles + 1) / 2));
+  pl.n_split = (int)std::min<int64_t>(s, 64);
+  pl.ws = sizeof(float) * ((size_t)R * p->H * kw + (size_t)pl.n_split * R * p->H * (p->rank + 2));
+  return pl;
+}
+
 }  // namespace
 
 extern "C" int evo_latent_prep(const evo_latent_prep_params* p, void* stream) {
@@ -203,17 +382,47 @@ extern "C" int evo_latent_prep(const evo_latent_prep_params* p, void* stream) {
   return check_launch("evo_latent_prep");
 }
 
-extern "C" int evo_latent_attn_decode(const evo_latent_decode_params* p, void* stream) {
+extern "C" size_t evo_latent_attn_decode_workspace(const evo_latent_decode_params* p) {
+  return split_plan(p).ws;
+}
+
+extern "C" int evo_latent_attn_decode(const evo_latent_decode_params* p, void* workspace, size_t workspace_bytes, void* stream) {
   EVO_REQUIRE(p->q && p->cache && p->uk && p->uv && p->out, "evo_latent_attn_decode: null argument");
   EVO_REQUIRE(p->H > 0 && p->dim > 0 && p->rot >= 0 && p->rank > 0 && p->vdim > 0 && p->rank_pad >= p->rank, "evo_latent_attn_decode: bad shape");
-  EVO_REQUIRE(p->rank <= RPT * DT, "evo_latent_attn_decode: latent size (%d) must be <= %d", p->rank, RPT * DT);
   EVO_REQUIRE(p->ldo >= (int64_t)p->H * p->vdim && p->H <= 65535 && p->B <= 65535, "evo_latent_attn_decode: bad output stride or grid");
   if ((int64_t)p->B * p->Lq == 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  const SplitPlan pl = split_plan(p);
+  if (pl.hg && workspace && workspace_bytes >= pl.ws) {
+    const int64_t R = (int64_t)p->B * p->Lq;
+    EVO_REQUIRE(R <= 65535, "evo_latent_attn_decode: too many query rows");
+    const int kw = p->rank + p->rot;
+    float* ql = (float*)workspace;
+    float* part = ql + (size_t)R * p->H * kw;
+    const size_t sm_a = sizeof(float) * AR * p->dim;
+    dim3 ga((unsigned)p->H, (unsigned)((p->rank + 127) / 128));
+    dim3 gs((unsigned)pl.n_split, (unsigned)R, (unsigned)((p->H + pl.hg - 1) / pl.hg));
+    dim3 gm((unsigned)R, (unsigned)p->H);
+    const size_t sm_m = sizeof(float) * p->rank;
+#define EVO_LATENT_SPLIT(T)                                                                                                          \
+    latent_absorb_kernel<T><<<ga, 128, sm_a, st>>>(*p, ql);                                                                          \
+    if (pl.hg == 16) {                                                                                                               \
+      if (pl.smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(latent_split_kernel<T, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem)); \
+      latent_split_kernel<T, 16><<<gs, SPLIT_T, pl.smem, st>>>(*p, ql, part, pl.n_split);                                           \
+    } else {                                                                                                                         \
+      if (pl.smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(latent_split_kernel<T, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));  \
+      latent_split_kernel<T, 8><<<gs, SPLIT_T, pl.smem, st>>>(*p, ql, part, pl.n_split);                                            \
+    }                                                                                                                                \
+    latent_merge_kernel<T><<<gm, 256, sm_m, st>>>(*p, part, pl.n_split);
+    if (p->dtype) { EVO_LATENT_SPLIT(float) } else { EVO_LATENT_SPLIT(bf16) }
+#undef EVO_LATENT_SPLIT
+    return check_launch("evo_latent_attn_decode");
+  }
+  EVO_REQUIRE(p->rank <= RPT * DT, "evo_latent_attn_decode: latent size (%d) must be <= %d", p->rank, RPT * DT);
   const int nr = p->rank >= DT ? DT : (p->rank + 31) / 32 * 32;
   const int ngrp = DT / nr;
   const size_t smem = sizeof(float) * ((size_t)p->dim + p->rot + p->rank + KC + (size_t)ngrp * p->rank);
   EVO_REQUIRE(smem <= 200 * 1024, "evo_latent_attn_decode: head too large for shared memory (%zu bytes)", smem);
-  cudaStream_t st = (cudaStream_t)stream;
   dim3 grid((unsigned)p->Lq, (unsigned)p->H, (unsigned)p->B);
   if (p->dtype) {
     if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(latent_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

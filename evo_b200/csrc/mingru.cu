@@ -6,8 +6,8 @@
 // The recurrence is linear in S, S_t = p_t S_{t-1} + q_t, so a sequence is cut into chunks of CH tokens: a first kernel reduces every
 // chunk to its (product of p, end value from a zero start), a second kernel folds the chunks before its own into the carried-in
 // state (a few fused multiply-adds per chunk) and then walks its chunk token by token, writing the outputs.  z and u are read
-// twice, g and the output once; the single-token step and short portions run the second kernel alone.  One thread owns one
-// channel of one chunk, consecutive threads consecutive channels (coalesced rows).
+// twice, g and the output once; the single-token step and short portions run the second kernel alone.  One thread owns two adjacent
+// channels of one chunk (one when sizes or alignment forbid), consecutive threads consecutive channels (coalesced rows).
 #include "common.cuh"
 #include "../../include/evo_b200.h"
 
@@ -23,7 +23,7 @@ template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p =
 template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
 constexpr int CH = 64;        // tokens per chunk
-constexpr int TPB = 128;      // channels per CTA
+constexpr int TPB = 128;      // threads per CTA
 
 __device__ __forceinline__ float sigmoidf_(float v) { return 1.f / (1.f + expf(-v)); }
 
@@ -36,58 +36,99 @@ __device__ __forceinline__ void gate_pair(float z, float u, float bz, float bu, 
   qq = a * cand;
 }
 
-template <typename T>
+// two adjacent channels of a row as floats (4-byte bf16 / 8-byte fp32 accesses), or one when VW == 1
+template <typename T, int VW> struct Ch;
+template <typename T> struct Ch<T, 1> {
+  static __device__ __forceinline__ void ld(const T* p, float* o) { o[0] = ldf(p); }
+  static __device__ __forceinline__ void st(T* p, const float* v) { stf(p, v[0]); }
+};
+template <> struct Ch<bf16, 2> {
+  static __device__ __forceinline__ void ld(const bf16* p, float* o) { const uint32_t u = *reinterpret_cast<const uint32_t*>(p); o[0] = bf_lo(u); o[1] = bf_hi(u); }
+  static __device__ __forceinline__ void st(bf16* p, const float* v) { *reinterpret_cast<uint32_t*>(p) = pack_bf16(v[0], v[1]); }
+};
+template <> struct Ch<float, 2> {
+  static __device__ __forceinline__ void ld(const float* p, float* o) { const float2 u = *reinterpret_cast<const float2*>(p); o[0] = u.x; o[1] = u.y; }
+  static __device__ __forceinline__ void st(float* p, const float* v) { *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]); }
+};
+
+template <typename T, int VW>
 __global__ void __launch_bounds__(TPB) mingru_chunk_kernel(evo_mingru_params p, int64_t chunk, int n_chunks, float2* __restrict__ agg, float* __restrict__ init) {
-  const int ch = blockIdx.x * TPB + threadIdx.x;
+  const int ch = (blockIdx.x * TPB + threadIdx.x) * VW;
   if (ch >= p.W) return;
   const int c = blockIdx.y, b = blockIdx.z;
   const int64_t t0 = (int64_t)c * chunk, t1 = min(p.L, t0 + chunk);
-  const float bz = p.z_bias ? __bfloat162float(((const bf16*)p.z_bias)[ch]) : 0.f;
-  const float bu = p.u_bias ? __bfloat162float(((const bf16*)p.u_bias)[ch]) : 0.f;
+  float bz[VW], bu[VW], P[VW], S[VW];
+#pragma unroll
+  for (int k = 0; k < VW; ++k) {
+    bz[k] = p.z_bias ? __bfloat162float(((const bf16*)p.z_bias)[ch + k]) : 0.f;
+    bu[k] = p.u_bias ? __bfloat162float(((const bf16*)p.u_bias)[ch + k]) : 0.f;
+    // the carried-in state is copied aside: the second kernel's last chunk overwrites p.state while other chunks may not have started
+    if (c == 0) init[(int64_t)b * p.W + ch + k] = (p.state && !p.zero_start) ? p.state[(int64_t)b * p.W + ch + k] : 0.f;
+    P[k] = 1.f; S[k] = 0.f;
+  }
   const T* z = (const T*)p.z + ((int64_t)b * p.L + t0) * p.ld + ch;
   const T* u = (const T*)p.u + ((int64_t)b * p.L + t0) * p.ld + ch;
-  // the carried-in state is copied aside: the second kernel's last chunk overwrites p.state while other chunks may not have started
-  if (c == 0) init[(int64_t)b * p.W + ch] = (p.state && !p.zero_start) ? p.state[(int64_t)b * p.W + ch] : 0.f;
-  float P = 1.f, S = 0.f;
 #pragma unroll 4
   for (int64_t t = t0; t < t1; ++t, z += p.ld, u += p.ld) {
-    float pp, qq;
-    gate_pair(ldf(z), ldf(u), bz, bu, pp, qq);
-    S = fmaf(pp, S, qq);
-    P *= pp;
+    float zv[VW], uv[VW];
+    Ch<T, VW>::ld(z, zv); Ch<T, VW>::ld(u, uv);
+#pragma unroll
+    for (int k = 0; k < VW; ++k) {
+      float pp, qq;
+      gate_pair(zv[k], uv[k], bz[k], bu[k], pp, qq);
+      S[k] = fmaf(pp, S[k], qq);
+      P[k] *= pp;
+    }
   }
-  agg[((int64_t)b * n_chunks + c) * p.W + ch] = make_float2(P, S);
+#pragma unroll
+  for (int k = 0; k < VW; ++k) agg[((int64_t)b * n_chunks + c) * p.W + ch + k] = make_float2(P[k], S[k]);
 }
 
-template <typename T>
+template <typename T, int VW>
 __global__ void __launch_bounds__(TPB) mingru_apply_kernel(evo_mingru_params p, int64_t chunk, int n_chunks, const float2* __restrict__ agg, const float* __restrict__ init) {
-  const int ch = blockIdx.x * TPB + threadIdx.x;
+  const int ch = (blockIdx.x * TPB + threadIdx.x) * VW;
   const int c = blockIdx.y, b = blockIdx.z;
   const int64_t t0 = (int64_t)c * chunk, t1 = min(p.L, t0 + chunk);
   T* o = (T*)p.out + ((int64_t)b * p.L + t0) * p.ldo + ch;
-  if (ch >= p.W) {                          // pad columns of the output
-    if (ch < p.ldo) for (int64_t t = t0; t < t1; ++t, o += p.ldo) stf(o, 0.f);
+  if (ch >= p.W) {                          // pad columns of the output (W and ldo are even when VW == 2)
+    const float zero[2] = {0.f, 0.f};
+    if (ch < p.ldo) for (int64_t t = t0; t < t1; ++t, o += p.ldo) Ch<T, VW>::st(o, zero);
     return;
   }
-  const float bz = p.z_bias ? __bfloat162float(((const bf16*)p.z_bias)[ch]) : 0.f;
-  const float bu = p.u_bias ? __bfloat162float(((const bf16*)p.u_bias)[ch]) : 0.f;
-  float S = n_chunks > 1 ? init[(int64_t)b * p.W + ch] : ((p.state && !p.zero_start) ? p.state[(int64_t)b * p.W + ch] : 0.f);
-  for (int k = 0; k < c; ++k) {
-    const float2 a = agg[((int64_t)b * n_chunks + k) * p.W + ch];
-    S = fmaf(a.x, S, a.y);
+  float bz[VW], bu[VW], S[VW];
+#pragma unroll
+  for (int k = 0; k < VW; ++k) {
+    bz[k] = p.z_bias ? __bfloat162float(((const bf16*)p.z_bias)[ch + k]) : 0.f;
+    bu[k] = p.u_bias ? __bfloat162float(((const bf16*)p.u_bias)[ch + k]) : 0.f;
+    S[k] = n_chunks > 1 ? init[(int64_t)b * p.W + ch + k] : ((p.state && !p.zero_start) ? p.state[(int64_t)b * p.W + ch + k] : 0.f);
+  }
+  for (int j = 0; j < c; ++j) {
+#pragma unroll
+    for (int k = 0; k < VW; ++k) {
+      const float2 a = agg[((int64_t)b * n_chunks + j) * p.W + ch + k];
+      S[k] = fmaf(a.x, S[k], a.y);
+    }
   }
   const T* z = (const T*)p.z + ((int64_t)b * p.L + t0) * p.ld + ch;
   const T* u = (const T*)p.u + ((int64_t)b * p.L + t0) * p.ld + ch;
   const T* g = (const T*)p.g + ((int64_t)b * p.L + t0) * p.ld + ch;
 #pragma unroll 4
   for (int64_t t = t0; t < t1; ++t, z += p.ld, u += p.ld, g += p.ld, o += p.ldo) {
-    float pp, qq;
-    gate_pair(ldf(z), ldf(u), bz, bu, pp, qq);
-    S = fmaf(pp, S, qq);
-    const float gv = ldf(g);
-    stf(o, S * (gv * sigmoidf_(gv)));
+    float zv[VW], uv[VW], gv[VW], ov[VW];
+    Ch<T, VW>::ld(z, zv); Ch<T, VW>::ld(u, uv); Ch<T, VW>::ld(g, gv);
+#pragma unroll
+    for (int k = 0; k < VW; ++k) {
+      float pp, qq;
+      gate_pair(zv[k], uv[k], bz[k], bu[k], pp, qq);
+      S[k] = fmaf(pp, S[k], qq);
+      ov[k] = S[k] * (gv[k] * sigmoidf_(gv[k]));
+    }
+    Ch<T, VW>::st(o, ov);
   }
-  if (c == n_chunks - 1 && p.state) p.state[(int64_t)b * p.W + ch] = S;
+  if (c == n_chunks - 1 && p.state) {
+#pragma unroll
+    for (int k = 0; k < VW; ++k) p.state[(int64_t)b * p.W + ch + k] = S[k];
+  }
 }
 
 inline void plan(const evo_mingru_params* p, int64_t& chunk, int& n_chunks) {
@@ -116,14 +157,18 @@ extern "C" int evo_mingru_fwd(const evo_mingru_params* p, void* workspace, size_
   cudaStream_t st = (cudaStream_t)stream;
   float2* agg = (float2*)workspace;
   float* init = n_chunks > 1 ? (float*)(agg + (size_t)p->B * n_chunks * p->W) : nullptr;
+  const int esz = p->dtype ? 4 : 2;
+  auto al = [esz](const void* q) { return ((uintptr_t)q & (uintptr_t)(2 * esz - 1)) == 0; };
+  const bool two = p->W % 2 == 0 && p->ld % 2 == 0 && p->ldo % 2 == 0 && al(p->z) && al(p->u) && al(p->g) && al(p->out);
+  const int per = TPB * (two ? 2 : 1);
   if (n_chunks > 1) {
-    dim3 grid((unsigned)((p->W + TPB - 1) / TPB), (unsigned)n_chunks, (unsigned)p->B);
-    if (p->dtype) mingru_chunk_kernel<float><<<grid, TPB, 0, st>>>(*p, chunk, n_chunks, agg, init);
-    else mingru_chunk_kernel<bf16><<<grid, TPB, 0, st>>>(*p, chunk, n_chunks, agg, init);
+    dim3 grid((unsigned)((p->W + per - 1) / per), (unsigned)n_chunks, (unsigned)p->B);
+    if (p->dtype) { if (two) mingru_chunk_kernel<float, 2><<<grid, TPB, 0, st>>>(*p, chunk, n_chunks, agg, init); else mingru_chunk_kernel<float, 1><<<grid, TPB, 0, st>>>(*p, chunk, n_chunks, agg, init); }
+    else { if (two) mingru_chunk_kernel<bf16, 2><<<grid, TPB, 0, st>>>(*p, chunk, n_chunks, agg, init); else mingru_chunk_kernel<bf16, 1><<<grid, TPB, 0, st>>>(*p, chunk, n_chunks, agg, init); }
     if (int rc = check_launch("evo_mingru_fwd")) return rc;
   }
-  dim3 grid((unsigned)((p->ldo + TPB - 1) / TPB), (unsigned)n_chunks, (unsigned)p->B);
-  if (p->dtype) mingru_apply_kernel<float><<<grid, TPB, 0, st>>>(*p, chunk, n_chunks, agg, init);
-  else mingru_apply_kernel<bf16><<<grid, TPB, 0, st>>>(*p, chunk, n_chunks, agg, init);
+  dim3 grid((unsigned)((p->ldo + per - 1) / per), (unsigned)n_chunks, (unsigned)p->B);
+  if (p->dtype) { if (two) mingru_apply_kernel<float, 2><<<grid, TPB, 0, st>>>(*p, chunk, n_chunks, agg, init); else mingru_apply_kernel<float, 1><<<grid, TPB, 0, st>>>(*p, chunk, n_chunks, agg, init); }
+  else { if (two) mingru_apply_kernel<bf16, 2><<<grid, TPB, 0, st>>>(*p, chunk, n_chunks, agg, init); else mingru_apply_kernel<bf16, 1><<<grid, TPB, 0, st>>>(*p, chunk, n_chunks, agg, init); }
   return check_launch("evo_mingru_fwd");
 }

@@ -15,8 +15,15 @@ template <> __device__ __forceinline__ float ldf<float>(const float* p) { return
 template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
 
 constexpr int RW = 4;         // warps (tokens) per CTA
+constexpr int EB = 16;        // experts whose partial sums a lane keeps at a time
 
-template <typename T>
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const bf16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  return make_float4(bf_lo(u.x), bf_hi(u.x), bf_lo(u.y), bf_hi(u.y));
+}
+
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(RW * 32) moe_route_kernel(const T* __restrict__ h, int64_t ldh, const bf16* __restrict__ rw, const bf16* __restrict__ corr,
                                                             float* __restrict__ weights, int32_t* __restrict__ chosen, int64_t rows, int D, int E, int top, float scale) {
   extern __shared__ float sm[];
@@ -26,15 +33,41 @@ __global__ void __launch_bounds__(RW * 32) moe_route_kernel(const T* __restrict_
   float* s = sm + (size_t)w * 2 * E;        // scores
   float* c = s + E;                         // choice scores (-inf once taken)
   const T* hr = h + row * ldh;
+  // logits: the lanes split the row; EB experts share every load of h (their partial sums stay in registers until the row ends)
   float mx = -INFINITY;
-  for (int e = 0; e < E; ++e) {
-    const bf16* wr = rw + (int64_t)e * D;
-    float d = 0.f;
-    for (int k = lane; k < D; k += 32) d = fmaf(ldf(hr + k), __bfloat162float(wr[k]), d);
+  for (int e0 = 0; e0 < E; e0 += EB) {
+    float acc[EB];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-    if (lane == 0) s[e] = d;
-    mx = fmaxf(mx, d);
+    for (int j = 0; j < EB; ++j) acc[j] = 0.f;
+    if (VEC) {                               // D % 4 == 0, 8-byte (bf16) / 16-byte (fp32) aligned rows
+      for (int k = lane * 4; k < D; k += 128) {
+        const float4 h4 = ld4(hr + k);
+#pragma unroll
+        for (int j = 0; j < EB; ++j) {
+          if (e0 + j < E) {
+            const float4 w4 = ld4(rw + (int64_t)(e0 + j) * D + k);
+            acc[j] = fmaf(h4.x, w4.x, fmaf(h4.y, w4.y, fmaf(h4.z, w4.z, fmaf(h4.w, w4.w, acc[j]))));
+          }
+        }
+      }
+    } else {
+      for (int k = lane; k < D; k += 32) {
+        const float hv = ldf(hr + k);
+#pragma unroll
+        for (int j = 0; j < EB; ++j)
+          if (e0 + j < E) acc[j] = fmaf(hv, __bfloat162float(rw[(int64_t)(e0 + j) * D + k]), acc[j]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < EB; ++j) {
+      float d = acc[j];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+      if (e0 + j < E) {
+        if (lane == 0) s[e0 + j] = d;
+        mx = fmaxf(mx, d);
+      }
+    }
   }
   __syncwarp();
   float sum = 0.f;
@@ -78,7 +111,13 @@ extern "C" int evo_moe_route(const void* h, int64_t ldh, const void* router_w, c
   const size_t smem = sizeof(float) * RW * 2 * (size_t)E;
   dim3 grid((unsigned)((rows + RW - 1) / RW)), block(RW * 32);
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype) moe_route_kernel<float><<<grid, block, smem, st>>>((const float*)h, ldh, (const bf16*)router_w, (const bf16*)correction, weights, chosen, rows, D, E, top, scale);
-  else moe_route_kernel<bf16><<<grid, block, smem, st>>>((const bf16*)h, ldh, (const bf16*)router_w, (const bf16*)correction, weights, chosen, rows, D, E, top, scale);
+  const bool vec = D % 4 == 0 && ldh % 4 == 0 && ((uintptr_t)h & (dtype ? 15 : 7)) == 0 && ((uintptr_t)router_w & 7) == 0;
+  if (dtype) {
+    if (vec) moe_route_kernel<float, true><<<grid, block, smem, st>>>((const float*)h, ldh, (const bf16*)router_w, (const bf16*)correction, weights, chosen, rows, D, E, top, scale);
+    else moe_route_kernel<float, false><<<grid, block, smem, st>>>((const float*)h, ldh, (const bf16*)router_w, (const bf16*)correction, weights, chosen, rows, D, E, top, scale);
+  } else {
+    if (vec) moe_route_kernel<bf16, true><<<grid, block, smem, st>>>((const bf16*)h, ldh, (const bf16*)router_w, (const bf16*)correction, weights, chosen, rows, D, E, top, scale);
+    else moe_route_kernel<bf16, false><<<grid, block, smem, st>>>((const bf16*)h, ldh, (const bf16*)router_w, (const bf16*)correction, weights, chosen, rows, D, E, top, scale);
+  }
   return check_launch("evo_moe_route");
 }

@@ -27,6 +27,7 @@ __device__ __forceinline__ float4 ld4(const bf16* p) {
 __device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
 __device__ __forceinline__ void st4(bf16* p, float4 v) { *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w)); }
 inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+inline bool aligned_to(const void* p, int n) { return ((uintptr_t)p & (uintptr_t)(n - 1)) == 0; }
 
 // sum over the block (blockDim.x <= 1024, a multiple of 32); every thread gets the total
 __device__ __forceinline__ float block_sum(float v, float* red) {
@@ -360,7 +361,10 @@ __device__ __forceinline__ float gated_value(const T* yr, const T* gr, const bf1
 
 // One CTA per row:  u = y * sigmoid(gate + gate_bias);  u <- u / rms(u) * post_gain (post_norm);  x <- x + u  (or u + row_add when
 // replace);  then out = x / rms(x) * gain, or (concat) out = [x | cat_row] cast without a norm.  All sums fp32.
-template <typename T>
+// VEC: 4 channels per access (D and every row stride a multiple of 4 elements, 16-byte aligned bases).
+__device__ __forceinline__ float sigm(float v) { return 1.f / (1.f + expf(-v)); }
+
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) branch_norm_kernel(evo_branch_norm_params p) {
   __shared__ float red[32];
   const int64_t r = blockIdx.x;
@@ -372,35 +376,94 @@ __global__ void __launch_bounds__(256) branch_norm_kernel(evo_branch_norm_params
   const bf16* gb = (const bf16*)p.gate_bias;
   const bf16* ra = (const bf16*)p.row_add;
   const bool write_back = p.gather == nullptr && (yr != nullptr || ra != nullptr);
+  constexpr int VW = VEC ? 4 : 1;
+  // u of channels [c, c + VW)
+  auto gated = [&](int c, float* u) {
+    if (VEC) {
+      const float4 y4 = ld4(yr + c);
+      u[0] = y4.x; u[1] = y4.y; u[2] = y4.z; u[3] = y4.w;
+      if (gr) {
+        const float4 g4 = ld4(gr + c);
+        float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (gb) b4 = ld4(gb + c);
+        u[0] *= sigm(g4.x + b4.x); u[1] *= sigm(g4.y + b4.y); u[2] *= sigm(g4.z + b4.z); u[3] *= sigm(g4.w + b4.w);
+      }
+    } else {
+      u[0] = gated_value(yr, gr, gb, c);
+    }
+  };
   float mul = 1.f;
   if (yr && p.post_norm) {
     float su = 0.f;
-    for (int c = threadIdx.x; c < D; c += blockDim.x) { const float u = gated_value(yr, gr, gb, c); su = fmaf(u, u, su); }
+    for (int c = threadIdx.x * VW; c < D; c += blockDim.x * VW) {
+      float u[VW];
+      gated(c, u);
+#pragma unroll
+      for (int k = 0; k < VW; ++k) su = fmaf(u[k], u[k], su);
+    }
     su = block_sum(su, red);
     mul = p.post_gain / sqrtf(su / (float)D + p.eps);
   }
-  auto value = [&](int c) {
-    float v = p.replace ? 0.f : xr[c];
-    if (yr) v = fmaf(gated_value(yr, gr, gb, c), mul, v);
-    if (ra) v += __bfloat162float(ra[c]);
-    return v;
+  auto value = [&](int c, float* v) {
+    if (p.replace) {
+#pragma unroll
+      for (int k = 0; k < VW; ++k) v[k] = 0.f;
+    } else if (VEC) {
+      const float4 x4 = ld4(xr + c);
+      v[0] = x4.x; v[1] = x4.y; v[2] = x4.z; v[3] = x4.w;
+    } else {
+      v[0] = xr[c];
+    }
+    if (yr) {
+      float u[VW];
+      gated(c, u);
+#pragma unroll
+      for (int k = 0; k < VW; ++k) v[k] = fmaf(u[k], mul, v[k]);
+    }
+    if (ra) {
+      if (VEC) { const float4 a4 = ld4(ra + c); v[0] += a4.x; v[1] += a4.y; v[2] += a4.z; v[3] += a4.w; }
+      else v[0] += __bfloat162float(ra[c]);
+    }
+  };
+  auto stream = [&](int c, float* v) {       // the row after the update: what this thread wrote back, else rebuilt
+    if (!write_back) { value(c, v); return; }
+    if (VEC) { const float4 x4 = ld4(xr + c); v[0] = x4.x; v[1] = x4.y; v[2] = x4.z; v[3] = x4.w; }
+    else v[0] = xr[c];
   };
   float ss = 0.f;
-  for (int c = threadIdx.x; c < D; c += blockDim.x) {
-    const float v = value(c);
-    if (write_back) xr[c] = v;
-    ss = fmaf(v, v, ss);
+  for (int c = threadIdx.x * VW; c < D; c += blockDim.x * VW) {
+    float v[VW];
+    value(c, v);
+    if (write_back) {
+      if (VEC) st4(xr + c, make_float4(v[0], v[1], v[2], v[3]));
+      else xr[c] = v[0];
+    }
+#pragma unroll
+    for (int k = 0; k < VW; ++k) ss = fmaf(v[k], v[k], ss);
   }
   if (!p.out) return;
   T* orow = (T*)p.out + r * p.ldo;
-  if (p.concat) {                           // a thread reads back only elements it wrote itself
-    const float* cr = p.cat + srow * D;
-    for (int c = threadIdx.x; c < p.ldo; c += blockDim.x) stf(orow + c, c < D ? (write_back ? xr[c] : value(c)) : (c < 2 * D ? cr[c - D] : 0.f));
-    return;
+  float g = 1.f;
+  const float* cr = p.concat ? p.cat + srow * D : nullptr;
+  if (!p.concat) {
+    ss = block_sum(ss, red);
+    g = p.gain / sqrtf(ss / (float)D + p.eps);
   }
-  ss = block_sum(ss, red);
-  const float g = p.gain / sqrtf(ss / (float)D + p.eps);
-  for (int c = threadIdx.x; c < p.ldo; c += blockDim.x) stf(orow + c, c < D ? (write_back ? xr[c] : value(c)) * g : 0.f);
+  for (int c = threadIdx.x * VW; c < p.ldo; c += blockDim.x * VW) {
+    float v[VW];
+#pragma unroll
+    for (int k = 0; k < VW; ++k) v[k] = 0.f;
+    if (c < D) {
+      stream(c, v);
+#pragma unroll
+      for (int k = 0; k < VW; ++k) v[k] *= g;
+    } else if (cr && c < 2 * D) {
+      if (VEC) { const float4 c4 = ld4(cr + c - D); v[0] = c4.x; v[1] = c4.y; v[2] = c4.z; v[3] = c4.w; }
+      else v[0] = cr[c - D];
+    }
+    if (VEC) st4(orow + c, make_float4(v[0], v[1], v[2], v[3]));
+    else stf(orow + c, v[0]);
+  }
 }
 
 __device__ __forceinline__ float act_value(float z, int act) {
@@ -411,23 +474,36 @@ __device__ __forceinline__ float act_value(float z, int act) {
   return z / (1.f + expf(-z));             // silu
 }
 
-// out[r, c] = act(g[r, c]) * u[r, c] * w(r, c) for c < F, zero for F <= c < ldo;  w = group_w[r, c / group] for c < n_groups * group, else 1
-template <typename T>
+// out[r, c] = act(g[r, c]) * u[r, c] * w(r, c) for c < F, zero for F <= c < ldo;  w = group_w[r, c / group] for c < n_groups * group, else 1.
+// grid (rows, column chunks): few rows (a decoding step) still fill the GPU.  VEC: 4 columns per thread (F, group, strides multiples of 4).
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) glu_act_kernel(const T* __restrict__ g, const T* __restrict__ u, int64_t ld, T* __restrict__ out, int64_t ldo,
                                                       int F, int act, const float* __restrict__ group_w, int group, int n_groups) {
   const int64_t r = blockIdx.x;
   const T* gr = g + r * ld; const T* ur = u + r * ld;
   T* orow = out + r * ldo;
   const float* wr = group_w ? group_w + r * n_groups : nullptr;
-  for (int c = threadIdx.x; c < ldo; c += blockDim.x) {
-    float v = 0.f;
-    if (c < F) {
-      float wt = 1.f;
-      if (wr) { const int e = c / group; if (e < n_groups) wt = wr[e]; }
-      v = wt == 0.f ? 0.f : act_value(ldf(gr + c), act) * ldf(ur + c) * wt;
+  constexpr int VW = VEC ? 4 : 1;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * VW;
+  if (c >= ldo) return;
+  float v[VW];
+#pragma unroll
+  for (int k = 0; k < VW; ++k) v[k] = 0.f;
+  if (c < F) {
+    float wt = 1.f;
+    if (wr) { const int e = c / group; if (e < n_groups) wt = wr[e]; }
+    if (wt != 0.f) {
+      if (VEC) {
+        const float4 g4 = ld4(gr + c), u4 = ld4(ur + c);
+        v[0] = act_value(g4.x, act) * u4.x * wt; v[1] = act_value(g4.y, act) * u4.y * wt;
+        v[2] = act_value(g4.z, act) * u4.z * wt; v[3] = act_value(g4.w, act) * u4.w * wt;
+      } else {
+        v[0] = act_value(ldf(gr + c), act) * ldf(ur + c) * wt;
+      }
     }
-    stf(orow + c, v);
   }
+  if (VEC) st4(orow + c, make_float4(v[0], v[1], v[2], v[3]));
+  else stf(orow + c, v[0]);
 }
 
 }  // namespace
@@ -451,8 +527,12 @@ extern "C" int evo_branch_norm(const evo_branch_norm_params* p, void* stream) {
   EVO_REQUIRE(!p->replace || p->y, "evo_branch_norm: replace without a branch output");
   if (p->rows == 0) return 0;
   dim3 grid((unsigned)p->rows), block(p->D >= 1024 ? 256 : 128);
-  if (p->dtype) branch_norm_kernel<float><<<grid, block, 0, (cudaStream_t)stream>>>(*p);
-  else branch_norm_kernel<bf16><<<grid, block, 0, (cudaStream_t)stream>>>(*p);
+  const int av = p->dtype ? 16 : 8;          // bytes of 4 activations
+  const bool vec = p->D % 4 == 0 && p->ldy % 4 == 0 && p->ldg % 4 == 0 && p->ldo % 4 == 0 && aligned16(p->x) && aligned_to(p->y, av) && aligned_to(p->gate, av) &&
+                   aligned_to(p->out, av) && aligned16(p->cat) && aligned_to(p->gate_bias, 8) && aligned_to(p->row_add, 8);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (p->dtype) { if (vec) branch_norm_kernel<float, true><<<grid, block, 0, st>>>(*p); else branch_norm_kernel<float, false><<<grid, block, 0, st>>>(*p); }
+  else { if (vec) branch_norm_kernel<bf16, true><<<grid, block, 0, st>>>(*p); else branch_norm_kernel<bf16, false><<<grid, block, 0, st>>>(*p); }
   return check_launch("evo_branch_norm");
 }
 
@@ -461,10 +541,19 @@ extern "C" int evo_glu_act(const void* gate, const void* up, int64_t ld, void* o
   EVO_REQUIRE(gate && up && out && F > 0 && ldo >= F && (act == 0 || act == 1), "evo_glu_act: bad arguments");
   EVO_REQUIRE(group_w == nullptr || (group > 0 && n_groups > 0), "evo_glu_act: bad groups");
   if (rows == 0) return 0;
-  dim3 grid((unsigned)rows), block(256);
+  const int av = dtype ? 16 : 8;
+  const bool vec = F % 4 == 0 && ld % 4 == 0 && ldo % 4 == 0 && (group_w == nullptr || group % 4 == 0) && aligned_to(gate, av) && aligned_to(up, av) && aligned_to(out, av);
+  const int per = 256 * (vec ? 4 : 1);
+  EVO_REQUIRE((ldo + per - 1) / per <= 65535, "evo_glu_act: row too wide");
+  dim3 grid((unsigned)rows, (unsigned)((ldo + per - 1) / per)), block(256);
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype) glu_act_kernel<float><<<grid, block, 0, st>>>((const float*)gate, (const float*)up, ld, (float*)out, ldo, F, act, group_w, group, n_groups);
-  else glu_act_kernel<bf16><<<grid, block, 0, st>>>((const bf16*)gate, (const bf16*)up, ld, (bf16*)out, ldo, F, act, group_w, group, n_groups);
+  if (dtype) {
+    if (vec) glu_act_kernel<float, true><<<grid, block, 0, st>>>((const float*)gate, (const float*)up, ld, (float*)out, ldo, F, act, group_w, group, n_groups);
+    else glu_act_kernel<float, false><<<grid, block, 0, st>>>((const float*)gate, (const float*)up, ld, (float*)out, ldo, F, act, group_w, group, n_groups);
+  } else {
+    if (vec) glu_act_kernel<bf16, true><<<grid, block, 0, st>>>((const bf16*)gate, (const bf16*)up, ld, (bf16*)out, ldo, F, act, group_w, group, n_groups);
+    else glu_act_kernel<bf16, false><<<grid, block, 0, st>>>((const bf16*)gate, (const bf16*)up, ld, (bf16*)out, ldo, F, act, group_w, group, n_groups);
+  }
   return check_launch("evo_glu_act");
 }
 

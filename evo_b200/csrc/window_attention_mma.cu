@@ -1,4 +1,4 @@
-// Tensor-core form of the windowed multi-map attention (see window_attention.cu for the mechanism) for bf16 activations.
+// Tensor-core form of the windowed attention with one or two score maps (see window_attention.cu for the mechanism) for bf16 activations.
 // The fp32 rule of the design is kept: scores are exact bf16 x bf16 products accumulated in fp32 (mma.sync m16n8k16), the softmax
 // runs in fp32 registers, and each probability enters P.V as a bf16 high part plus a bf16 low part (two MMAs, relative error
 // 2^-17 per weight instead of 2^-9), accumulated in fp32.
@@ -57,7 +57,7 @@ __device__ __forceinline__ void split_pack(float x, float y, uint32_t& hi, uint3
 }
 
 // NV8 = padded dv / 8 (output tiles of 8 channels per warp row block)
-template <int NV8>
+template <int NV8, int NM>
 __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_attn_params p, int dkp, int qst, int kst, int vst, int vec, int2 vstep) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [WARPS*16][qst]   both maps' queries
@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
   const int64_t rel0 = (int64_t)blockIdx.x * (WARPS * QROWS);
   // 16-byte copies of [row][both maps' dkp columns]: a row has c8n chunks, cpm per map; this thread's first (row, chunk) and its step
   // (vstep = 128 / c8n, 128 % c8n, from the host) replace a division per copy
-  const int cpm = dkp / 8, c8n = 2 * cpm, vr0 = tid / c8n, vc0 = tid % c8n;
+  const int cpm = dkp / 8, c8n = NM * cpm, vr0 = tid / c8n, vc0 = tid % c8n;
   const bf16* qg = (const bf16*)p.q;
   // queries of the CTA: [row][map][dkp], zero padding for rows past Lq and columns past dk
   const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
@@ -79,21 +79,21 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
       const int m = cc >= cpm, e = (cc - m * cpm) * 8;
       const int64_t rel = rel0 + r;
       uint4 v = zero4;
-      if (rel < p.Lq && e < dk) v = *reinterpret_cast<const uint4*>(qg + ((int64_t)b * p.Lq + rel) * p.q_tok_stride + (int64_t)h * 2 * dk + m * dk + e);
+      if (rel < p.Lq && e < dk) v = *reinterpret_cast<const uint4*>(qg + ((int64_t)b * p.Lq + rel) * p.q_tok_stride + (int64_t)h * NM * dk + m * dk + e);
       *reinterpret_cast<uint4*>(Qs + r * qst + cc * 8) = v;
       r += vstep.x; cc += vstep.y;
       if (cc >= c8n) { cc -= c8n; ++r; }
     }
   } else {
-    for (int idx = tid; idx < WARPS * QROWS * 2 * dkp; idx += WARPS * 32) {
-      const int r = idx / (2 * dkp), c = idx % (2 * dkp), m = c / dkp, e = c % dkp;
+    for (int idx = tid; idx < WARPS * QROWS * NM * dkp; idx += WARPS * 32) {
+      const int r = idx / (NM * dkp), c = idx % (NM * dkp), m = c / dkp, e = c % dkp;
       const int64_t rel = rel0 + r;
       bf16 v = __float2bfloat16_rn(0.f);
-      if (rel < p.Lq && e < dk) v = qg[((int64_t)b * p.Lq + rel) * p.q_tok_stride + (int64_t)h * 2 * dk + m * dk + e];
+      if (rel < p.Lq && e < dk) v = qg[((int64_t)b * p.Lq + rel) * p.q_tok_stride + (int64_t)h * NM * dk + m * dk + e];
       Qs[r * qst + c] = v;
     }
   }
-  const bf16* kb = (const bf16*)p.k + (int64_t)b * p.k_batch_stride + (int64_t)g * 2 * dk;
+  const bf16* kb = (const bf16*)p.k + (int64_t)b * p.k_batch_stride + (int64_t)g * NM * dk;
   const bf16* vb = (const bf16*)p.v + (int64_t)b * p.v_batch_stride + (int64_t)g * dv;
   const int64_t i_lo = pos + rel0, i_hi = pos + min(p.Lq - 1, rel0 + WARPS * QROWS - 1);
   const bool windowed = p.window > 0;
@@ -103,10 +103,10 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
   const int64_t i0 = pos + rel0 + w * QROWS + qr, i1 = i0 + 8;                // positions of the thread's two rows
   const int64_t wi_lo = pos + rel0 + w * QROWS, wi_hi = wi_lo + QROWS - 1;     // the warp's first / last position
 
-  float O[2][NV8][4];
-  float mrun[2][2], lrun[2][2];
+  float O[NM][NV8][4];
+  float mrun[NM][2], lrun[NM][2];
 #pragma unroll
-  for (int m = 0; m < 2; ++m) {
+  for (int m = 0; m < NM; ++m) {
     mrun[m][0] = mrun[m][1] = -INFINITY; lrun[m][0] = lrun[m][1] = 0.f;
 #pragma unroll
     for (int n = 0; n < NV8; ++n) O[m][n][0] = O[m][n][1] = O[m][n][2] = O[m][n][3] = 0.f;
@@ -135,8 +135,8 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
           *reinterpret_cast<uint4*>(Vs + r * vst + c) = v;
         }
       } else {
-        for (int idx = tid; idx < KT * 2 * dkp; idx += WARPS * 32) {
-          const int r = idx / (2 * dkp), c = idx % (2 * dkp), m = c / dkp, e = c % dkp;
+        for (int idx = tid; idx < KT * NM * dkp; idx += WARPS * 32) {
+          const int r = idx / (NM * dkp), c = idx % (NM * dkp), m = c / dkp, e = c % dkp;
           bf16 v = __float2bfloat16_rn(0.f);
           if (r < nk && e < dk) v = kb[(k0 + r) * p.k_tok_stride + m * dk + e];
           Ks[r * kst + c] = v;
@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
       const bool full = nk == KT && t_hi <= wi_lo && (!windowed || wi_hi - t_lo < p.window || t_hi < p.keep_first);
 
 #pragma unroll
-      for (int m = 0; m < 2; ++m) {
+      for (int m = 0; m < NM; ++m) {
         // scores of map m: S (16 x 64) = Q_m (16 x dkp) . K_m^T
         float Pm[1][KT / 8][4];
 #pragma unroll
@@ -241,14 +241,15 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
   }
   // o = a1 / l1 - lambda * a2 / l2, head norm, gate, store
   const int64_t rel_a = rel0 + w * QROWS + qr, rel_b = rel_a + 8;
-  const float il[2][2] = {{1.f / lrun[0][0], 1.f / lrun[0][1]}, {1.f / lrun[1][0], 1.f / lrun[1][1]}};
+  const float il[2][2] = {{1.f / lrun[0][0], 1.f / lrun[0][1]}, {1.f / lrun[NM - 1][0], 1.f / lrun[NM - 1][1]}};
   float ss0 = 0.f, ss1 = 0.f;
 #pragma unroll
   for (int n = 0; n < NV8; ++n) {
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       const int r = c >> 1;
-      const float v = O[0][n][c] * il[0][r] - p.lambda * (O[1][n][c] * il[1][r]);
+      float v = O[0][n][c] * il[0][r];
+      if (NM == 2) v -= p.lambda * (O[NM - 1][n][c] * il[1][r]);
       const bool live = n * 8 + qc + (c & 1) < dv;
       O[0][n][c] = live ? v : 0.f;
       if (r == 0) ss0 = fmaf(O[0][n][c], O[0][n][c], ss0); else ss1 = fmaf(O[0][n][c], O[0][n][c], ss1);
@@ -286,35 +287,40 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
   }
 }
 
-template <int NV8>
+template <int NV8, int NM>
 int launch(const evo_window_attn_params* p, cudaStream_t st) {
   const int dkp = (p->dk + 15) / 16 * 16;
-  const int qst = 2 * dkp + 8, kst = 2 * dkp + 8, vst = NV8 * 8 + 8;
+  const int qst = NM * dkp + 8, kst = NM * dkp + 8, vst = NV8 * 8 + 8;
   const size_t smem = sizeof(bf16) * ((size_t)WARPS * QROWS * qst + (size_t)KT * kst + (size_t)KT * vst);
   auto a16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
   const int vec = p->dk % 8 == 0 && p->dv % 8 == 0 && p->q_tok_stride % 8 == 0 && p->k_tok_stride % 8 == 0 && p->v_tok_stride % 8 == 0 &&
                   p->k_batch_stride % 8 == 0 && p->v_batch_stride % 8 == 0 && a16(p->q) && a16(p->k) && a16(p->v);
-  auto kern = window_attn_mma_kernel<NV8>;
+  auto kern = window_attn_mma_kernel<NV8, NM>;
   if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  const int c8n = 2 * dkp / 8;
+  const int c8n = NM * dkp / 8;
   kern<<<dim3((unsigned)((p->Lq + WARPS * QROWS - 1) / (WARPS * QROWS)), p->H, p->B), WARPS * 32, smem, st>>>(*p, dkp, qst, kst, vst, vec,
                                                                                                                  make_int2(WARPS * 32 / c8n, WARPS * 32 % c8n));
   return check_launch("evo_window_attn_fwd");
 }
 
+template <int NM>
+int dispatch(const evo_window_attn_params* p, cudaStream_t st) {
+  const int nv8 = (p->dv + 15) / 16 * 2;
+  switch (nv8) {
+    case 2: return launch<2, NM>(p, st);
+    case 4: return launch<4, NM>(p, st);
+    case 6: return launch<6, NM>(p, st);
+    case 8: return launch<8, NM>(p, st);
+    case 10: return launch<10, NM>(p, st);
+    case 12: return launch<12, NM>(p, st);
+    case 14: return launch<14, NM>(p, st);
+    default: return launch<16, NM>(p, st);
+  }
+}
+
 }  // namespace
 
 int evo::window_attn_mma(const evo_window_attn_params* p, cudaStream_t st) {
-  if (p->dtype != 0 || p->n_maps != 2 || p->dk > 128 || p->dv > 128 || p->dv % 8 != 0 || p->Lq < 16) return 1;
-  const int nv8 = (p->dv + 15) / 16 * 2;
-  switch (nv8) {
-    case 2: return launch<2>(p, st);
-    case 4: return launch<4>(p, st);
-    case 6: return launch<6>(p, st);
-    case 8: return launch<8>(p, st);
-    case 10: return launch<10>(p, st);
-    case 12: return launch<12>(p, st);
-    case 14: return launch<14>(p, st);
-    default: return launch<16>(p, st);
-  }
+  if (p->dtype != 0 || p->dk * p->n_maps > 256 || p->dk > 128 || p->dv > 128 || p->dv % 8 != 0 || p->Lq < 16) return 1;
+  return p->n_maps == 2 ? dispatch<2>(p, st) : dispatch<1>(p, st);
 }

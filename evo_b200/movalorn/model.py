@@ -21,6 +21,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 from typing import Optional
 
 import torch
@@ -50,6 +51,8 @@ class Movalorn(StreamDecoder):
 
     def __init__(self, config: MovalornConfig, dtype: torch.dtype = torch.bfloat16):
         super().__init__(config, dtype)
+        # few-row latent attention: "shared" = heads share each tile of latents (three launches), "head" = one CTA per (query, head)
+        self.latent_decode_path = os.environ.get("EVO_B200_LATENT_DECODE", "shared")
 
     # ---- parameters ----------------------------------------------------------------------------
     def init_random(self, seed: int = 0, device=None) -> "Movalorn":
@@ -198,9 +201,13 @@ class Movalorn(StreamDecoder):
             dp = LatentDecodeParams(q=z.data_ptr(), ldq=ld, cache=cache.data_ptr(), cache_row=cache_row, cache_batch_stride=bstride, rank_pad=rank_pad,
                                     uk=w[f"l{i}.mix.uk"].data_ptr(), uv=w[f"l{i}.mix.uv"].data_ptr(), gate=gate_ptr, ld_gate=ld,
                                     out=out.data_ptr(), ldo=ldo, B=B, Lq=L, H=m.heads, dim=m.dim, rot=m.rot_dim, rank=m.kv_rank, vdim=m.vdim,
-                                    pos0=off, pos_dev=pos_ptr, window=m.window, scale=m.scale, dtype=self._dt)
-            self._record("latent_decode", float(M) * m.heads * span * (m.kv_rank + m.rot_dim) * esz,
-                         lambda: check(lib.evo_latent_attn_decode(C.byref(dp), self._stream()), "evo_latent_attn_decode"))
+                                    pos0=off, pos_dev=pos_ptr, window=m.window, scale=m.scale, dtype=self._dt,
+                                    max_keys=cache.shape[1] if pos_dev is not None else off + L)
+            nws = lib.evo_latent_attn_decode_workspace(C.byref(dp)) if self.latent_decode_path == "shared" else 0
+            ws = torch.empty(nws, dtype=torch.uint8, device=dev) if nws else None
+            # roofline bytes: each sequence's visible latents once (all heads share them)
+            self._record("latent_decode", float(M) * span * (m.kv_rank + m.rot_dim) * esz,
+                         lambda: check(lib.evo_latent_attn_decode(C.byref(dp), ptr(ws), nws, self._stream()), "evo_latent_attn_decode"))
         else:
             lo = max(0, off - (m.window - 1)) if m.window > 0 else 0
             n = off + L - lo

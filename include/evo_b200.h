@@ -441,8 +441,11 @@ typedef struct {
   void* out; int64_t ldo;
   int B; int64_t Lq; int H, dim, rot, rank, vdim;
   int64_t pos0; const int64_t* pos_dev; int64_t window; float scale; int dtype;
+  int64_t max_keys;                           /* host bound on the keys a query can see (sizes the key splits); 0: unknown */
 } evo_latent_decode_params;
-int evo_latent_attn_decode(const evo_latent_decode_params* p, void* stream);
+/* workspace: evo_latent_attn_decode_workspace() bytes (absorbed queries and per-split partial sums); with less, the per-head kernel runs */
+size_t evo_latent_attn_decode_workspace(const evo_latent_decode_params* p);
+int evo_latent_attn_decode(const evo_latent_decode_params* p, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Expert router: logits = W (E, D) . h in fp32, s = softmax(logits), the `top` experts with the largest s + correction are chosen;
  * weights (rows, E) fp32 = s * scale for the chosen experts, 0 for the others; chosen (rows, top) int32 (optional). */

@@ -221,8 +221,9 @@ def _portions(model, tokens, sizes, max_seqlen=None, state=None):
     return torch.cat(outs, 0)
 
 
-@pytest.mark.parametrize("mode", ["prompt", "portions", "steps"])
-@pytest.mark.parametrize("H,dim,rd,vd,rank,window", [(3, 8, 4, 10, 12, 7), (1, 16, 8, 16, 40, 33), (2, 24, 2, 6, 9, 600), (5, 4, 12, 36, 130, 2)])
+@pytest.mark.parametrize("mode", ["prompt", "portions", "steps", "steps_per_head"])
+@pytest.mark.parametrize("H,dim,rd,vd,rank,window", [(3, 8, 4, 10, 12, 7), (1, 16, 8, 16, 40, 33), (2, 24, 2, 6, 9, 600), (5, 4, 12, 36, 130, 2), (13, 8, 6, 8, 70, 50),
+                                                     (9, 8, 4, 8, 600, 21)])
 def test_latent_attention_mixer_matches_the_oracle(mode, H, dim, rd, vd, rank, window):
     """The mixer alone (input rows -> projections -> cache -> attention -> output projection) against the oracle's token loop:
     the absorbed kernel (steps, short portions) and the expanded path (prompts) compute the same function."""
@@ -239,7 +240,9 @@ def test_latent_attention_mixer_matches_the_oracle(mode, H, dim, rd, vd, rank, w
     hd = h.to(DEV)
     mc = model.config.layers[0].mixer
     state = model.initialize_inference_params(max_seqlen=T, max_batch_size=1)
-    sizes = {"prompt": [T], "portions": [5, 2, 30, 3, T - 40], "steps": [T - 20] + [1] * 20}[mode]
+    sizes = {"prompt": [T], "portions": [5, 2, 30, 3, T - 40], "steps": [T - 20] + [1] * 20, "steps_per_head": [T - 24] + [1] * 20 + [4]}[mode]
+    if mode == "steps_per_head":
+        model.latent_decode_path = "head"
     outs, t = [], 0
     with torch.no_grad():
         for n in sizes:
