@@ -185,6 +185,11 @@ SIGNATURES = {
     "evo_latent_prep": (C.c_int, [C.POINTER(LatentPrepParams), C.c_void_p]),
     "evo_latent_attn_decode_workspace": (C.c_size_t, [C.POINTER(LatentDecodeParams)]),
     "evo_latent_attn_decode": (C.c_int, [C.POINTER(LatentDecodeParams), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "evo_moe_count": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
+    "evo_moe_scatter": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "evo_gather_rows": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
+    "evo_moe_combine": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                                  C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "evo_moe_route": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]),
 }
 

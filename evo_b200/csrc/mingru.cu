@@ -25,13 +25,17 @@ template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = _
 constexpr int CH = 64;        // tokens per chunk
 constexpr int TPB = 128;      // threads per CTA
 
-__device__ __forceinline__ float sigmoidf_(float v) { return 1.f / (1.f + expf(-v)); }
+// IEEE exp and division for fp32 activations (the all-fp32 mode); the hardware approximations (relative error ~1e-6) for bf16 ones
+template <typename T> __device__ __forceinline__ float sigmoidf_(float v);
+template <> __device__ __forceinline__ float sigmoidf_<float>(float v) { return 1.f / (1.f + expf(-v)); }
+template <> __device__ __forceinline__ float sigmoidf_<bf16>(float v) { return __fdividef(1.f, 1.f + __expf(-v)); }
 
 // (p, q) of one token: S <- p S + q
+template <typename T>
 __device__ __forceinline__ void gate_pair(float z, float u, float bz, float bu, float& pp, float& qq) {
-  const float a = sigmoidf_(z + bz);
+  const float a = sigmoidf_<T>(z + bz);
   const float c = u + bu;
-  const float cand = c >= 0.f ? c + 0.5f : sigmoidf_(c);
+  const float cand = c >= 0.f ? c + 0.5f : sigmoidf_<T>(c);
   pp = 1.f - a;
   qq = a * cand;
 }
@@ -68,14 +72,14 @@ __global__ void __launch_bounds__(TPB) mingru_chunk_kernel(evo_mingru_params p, 
   }
   const T* z = (const T*)p.z + ((int64_t)b * p.L + t0) * p.ld + ch;
   const T* u = (const T*)p.u + ((int64_t)b * p.L + t0) * p.ld + ch;
-#pragma unroll 4
+#pragma unroll 8
   for (int64_t t = t0; t < t1; ++t, z += p.ld, u += p.ld) {
     float zv[VW], uv[VW];
     Ch<T, VW>::ld(z, zv); Ch<T, VW>::ld(u, uv);
 #pragma unroll
     for (int k = 0; k < VW; ++k) {
       float pp, qq;
-      gate_pair(zv[k], uv[k], bz[k], bu[k], pp, qq);
+      gate_pair<T>(zv[k], uv[k], bz[k], bu[k], pp, qq);
       S[k] = fmaf(pp, S[k], qq);
       P[k] *= pp;
     }
@@ -89,7 +93,7 @@ __global__ void __launch_bounds__(TPB) mingru_apply_kernel(evo_mingru_params p, 
   const int ch = (blockIdx.x * TPB + threadIdx.x) * VW;
   const int c = blockIdx.y, b = blockIdx.z;
   const int64_t t0 = (int64_t)c * chunk, t1 = min(p.L, t0 + chunk);
-  T* o = (T*)p.out + ((int64_t)b * p.L + t0) * p.ldo + ch;
+  T* __restrict__ o = (T*)p.out + ((int64_t)b * p.L + t0) * p.ldo + ch;
   if (ch >= p.W) {                          // pad columns of the output (W and ldo are even when VW == 2)
     const float zero[2] = {0.f, 0.f};
     if (ch < p.ldo) for (int64_t t = t0; t < t1; ++t, o += p.ldo) Ch<T, VW>::st(o, zero);
@@ -109,9 +113,9 @@ __global__ void __launch_bounds__(TPB) mingru_apply_kernel(evo_mingru_params p, 
       S[k] = fmaf(a.x, S[k], a.y);
     }
   }
-  const T* z = (const T*)p.z + ((int64_t)b * p.L + t0) * p.ld + ch;
-  const T* u = (const T*)p.u + ((int64_t)b * p.L + t0) * p.ld + ch;
-  const T* g = (const T*)p.g + ((int64_t)b * p.L + t0) * p.ld + ch;
+  const T* __restrict__ z = (const T*)p.z + ((int64_t)b * p.L + t0) * p.ld + ch;
+  const T* __restrict__ u = (const T*)p.u + ((int64_t)b * p.L + t0) * p.ld + ch;
+  const T* __restrict__ g = (const T*)p.g + ((int64_t)b * p.L + t0) * p.ld + ch;
 #pragma unroll 4
   for (int64_t t = t0; t < t1; ++t, z += p.ld, u += p.ld, g += p.ld, o += p.ldo) {
     float zv[VW], uv[VW], gv[VW], ov[VW];
@@ -119,9 +123,9 @@ __global__ void __launch_bounds__(TPB) mingru_apply_kernel(evo_mingru_params p, 
 #pragma unroll
     for (int k = 0; k < VW; ++k) {
       float pp, qq;
-      gate_pair(zv[k], uv[k], bz[k], bu[k], pp, qq);
+      gate_pair<T>(zv[k], uv[k], bz[k], bu[k], pp, qq);
       S[k] = fmaf(pp, S[k], qq);
-      ov[k] = S[k] * (gv[k] * sigmoidf_(gv[k]));
+      ov[k] = S[k] * (gv[k] * sigmoidf_<T>(gv[k]));
     }
     Ch<T, VW>::st(o, ov);
   }

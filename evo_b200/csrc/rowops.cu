@@ -352,18 +352,22 @@ __global__ void embed_pair_kernel(const IdT* __restrict__ ids, const bf16* __res
   for (int c = threadIdx.x; c < D; c += blockDim.x) out[row * D + c] = fmaf(__bfloat162float(src[c]), scale, __bfloat162float(pr[c]));
 }
 
+// sigmoid and the two gate activations: IEEE exp / tanh / division for fp32 activations (the all-fp32 mode), the hardware
+// approximations (ex2, rcp: relative error ~1e-6) for bf16 activations, whose own rounding is 4e-3
+template <typename T> __device__ __forceinline__ float sigm(float v);
+template <> __device__ __forceinline__ float sigm<float>(float v) { return 1.f / (1.f + expf(-v)); }
+template <> __device__ __forceinline__ float sigm<bf16>(float v) { return __fdividef(1.f, 1.f + __expf(-v)); }
+
 template <typename T>
 __device__ __forceinline__ float gated_value(const T* yr, const T* gr, const bf16* gb, int c) {
   float u = ldf(yr + c);
-  if (gr) u *= 1.f / (1.f + expf(-(ldf(gr + c) + (gb ? __bfloat162float(gb[c]) : 0.f))));
+  if (gr) u *= sigm<T>(ldf(gr + c) + (gb ? __bfloat162float(gb[c]) : 0.f));
   return u;
 }
 
 // One CTA per row:  u = y * sigmoid(gate + gate_bias);  u <- u / rms(u) * post_gain (post_norm);  x <- x + u  (or u + row_add when
 // replace);  then out = x / rms(x) * gain, or (concat) out = [x | cat_row] cast without a norm.  All sums fp32.
 // VEC: 4 channels per access (D and every row stride a multiple of 4 elements, 16-byte aligned bases).
-__device__ __forceinline__ float sigm(float v) { return 1.f / (1.f + expf(-v)); }
-
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) branch_norm_kernel(evo_branch_norm_params p) {
   __shared__ float red[32];
@@ -386,7 +390,7 @@ __global__ void __launch_bounds__(256) branch_norm_kernel(evo_branch_norm_params
         const float4 g4 = ld4(gr + c);
         float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
         if (gb) b4 = ld4(gb + c);
-        u[0] *= sigm(g4.x + b4.x); u[1] *= sigm(g4.y + b4.y); u[2] *= sigm(g4.z + b4.z); u[3] *= sigm(g4.w + b4.w);
+        u[0] *= sigm<T>(g4.x + b4.x); u[1] *= sigm<T>(g4.y + b4.y); u[2] *= sigm<T>(g4.z + b4.z); u[3] *= sigm<T>(g4.w + b4.w);
       }
     } else {
       u[0] = gated_value(yr, gr, gb, c);
@@ -466,12 +470,14 @@ __global__ void __launch_bounds__(256) branch_norm_kernel(evo_branch_norm_params
   }
 }
 
+template <typename T>
 __device__ __forceinline__ float act_value(float z, int act) {
-  if (act == 0) {                         // tanh form of gelu
-    const float t = tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z));
-    return 0.5f * z * (1.f + t);
+  if (act == 0) {                         // tanh form of gelu: 0.5 z (1 + tanh(a)) = z sigmoid(2a)
+    const float a = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+    if (sizeof(T) == 4) return 0.5f * z * (1.f + tanhf(a));
+    return z * sigm<T>(2.f * a);
   }
-  return z / (1.f + expf(-z));             // silu
+  return z * sigm<T>(z);                   // silu
 }
 
 // out[r, c] = act(g[r, c]) * u[r, c] * w(r, c) for c < F, zero for F <= c < ldo;  w = group_w[r, c / group] for c < n_groups * group, else 1.
@@ -495,10 +501,10 @@ __global__ void __launch_bounds__(256) glu_act_kernel(const T* __restrict__ g, c
     if (wt != 0.f) {
       if (VEC) {
         const float4 g4 = ld4(gr + c), u4 = ld4(ur + c);
-        v[0] = act_value(g4.x, act) * u4.x * wt; v[1] = act_value(g4.y, act) * u4.y * wt;
-        v[2] = act_value(g4.z, act) * u4.z * wt; v[3] = act_value(g4.w, act) * u4.w * wt;
+        v[0] = act_value<T>(g4.x, act) * u4.x * wt; v[1] = act_value<T>(g4.y, act) * u4.y * wt;
+        v[2] = act_value<T>(g4.z, act) * u4.z * wt; v[3] = act_value<T>(g4.w, act) * u4.w * wt;
       } else {
-        v[0] = act_value(ldf(gr + c), act) * ldf(ur + c) * wt;
+        v[0] = act_value<T>(ldf(gr + c), act) * ldf(ur + c) * wt;
       }
     }
   }

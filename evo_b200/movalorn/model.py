@@ -53,6 +53,9 @@ class Movalorn(StreamDecoder):
         super().__init__(config, dtype)
         # few-row latent attention: "shared" = heads share each tile of latents (three launches), "head" = one CTA per (query, head)
         self.latent_decode_path = os.environ.get("EVO_B200_LATENT_DECODE", "shared")
+        # expert mixtures: calls with at least this many rows (outside a captured step) run only the chosen experts, one GEMM pair per
+        # expert over the rows sorted by expert (the per-expert row counts come back to the host); fewer rows run all experts densely
+        self.moe_sparse_min_rows = int(os.environ.get("EVO_B200_MOE_SPARSE_MIN_ROWS", "1024"))
 
     # ---- parameters ----------------------------------------------------------------------------
     def init_random(self, seed: int = 0, device=None) -> "Movalorn":
@@ -120,6 +123,7 @@ class Movalorn(StreamDecoder):
                 e["up"] = _Packed(torch.cat([w[f"{p}mlp.{n}.gate"] for n in names] + [w[f"{p}mlp.{n}.up"] for n in names] + [w[p + "rg2"]], 0))
                 e["down"] = _Packed(torch.cat([w[f"{p}mlp.{n}.down"] for n in names], 1))
                 e["hidden"] = f.experts * f.ff + f.shared_ff
+                e["sparse"] = None                  # per-expert packing, built on the first sparse call
             packed["layers"].append(e)
         self._packed = packed
         return packed
@@ -227,9 +231,76 @@ class Movalorn(StreamDecoder):
         y = self._linear(out, pk["out"], M)
         return _Pending(y, pk["out"].Np, z.data_ptr() + (qw + aw + m.heads) * esz, ld, w[f"l{i}.rg1.b"], self._packed["gain"][f"l{i}.norm1b"], hold=z)
 
-    def _feed_forward(self, i, f, h, M):
+    def _sparse_pack(self, i, f):
+        pk = self._packed["layers"][i]
+        if pk["sparse"] is None:
+            w, p = self.weights, f"l{i}.mlp."
+            sp = {"experts": [(_Packed(torch.cat([w[f"{p}e{k}.gate"], w[f"{p}e{k}.up"]], 0)), _Packed(w[f"{p}e{k}.down"])) for k in range(f.experts)]}
+            rest = ([w[p + "shared.gate"], w[p + "shared.up"]] if f.shared_ff else []) + [w[f"l{i}.rg2"]]
+            sp["rest"] = _Packed(torch.cat(rest, 0))
+            sp["shared_down"] = _Packed(w[p + "shared.down"]) if f.shared_ff else None
+            pk["sparse"] = sp
+        return pk["sparse"]
+
+    def _experts_sparse(self, i, f, h, M):
+        """Only the chosen experts: route, sort the (token, choice) pairs by expert, one [gate ; up] GEMM, activation and down GEMM per
+        expert over its slice, then the weighted sum per token on top of the always-on expert."""
+        sp = self._sparse_pack(i, f)
+        dev, w, lib, D = h.device, self.weights, _lib.lib(), self.config.width
+        E, top, n = f.experts, f.top, M * f.top
+        esz = h.element_size()
+        route = torch.empty(M, E, dtype=torch.float32, device=dev)
+        chosen = torch.full((M, top), -1, dtype=torch.int32, device=dev)
+        self._record("moe_route", float(M) * D * esz, lambda: check(lib.evo_moe_route(
+            ptr(h), h.shape[1], ptr(w[f"l{i}.mlp.router"]), ptr(w[f"l{i}.mlp.correction"]), ptr(route), ptr(chosen), M, D,
+            E, top, f.router_scale, self._dt, self._stream()), "evo_moe_route"))
+        counts = torch.zeros(2, E, dtype=torch.int32, device=dev)                      # row 0: counts, row 1: the scatter's cursors
+        check(lib.evo_moe_count(ptr(chosen), n, E, ptr(counts), self._stream()), "evo_moe_count")
+        cnt = counts[0].cpu()                                                           # the one host round trip of the layer
+        off = torch.zeros(E + 1, dtype=torch.int64)
+        off[1:] = torch.cumsum(cnt.to(torch.int64), 0)
+        offsets = off[:E].to(torch.int32).to(dev)
+        total = int(off[E])
+        perm = torch.empty(max(total, 1), dtype=torch.int32, device=dev)
+        slot_of = torch.empty(M, top, dtype=torch.int32, device=dev)
+        check(lib.evo_moe_scatter(ptr(chosen), n, top, E, ptr(offsets), C.c_void_p(counts.data_ptr() + 4 * E), ptr(perm), ptr(slot_of), self._stream()), "evo_moe_scatter")
+        Kp = h.shape[1]
+        hs = torch.empty(max(total, 1), Kp, dtype=self.act_dtype, device=dev)
+        self._record("moe_gather", 2.0 * total * Kp * esz, lambda: check(lib.evo_gather_rows(ptr(h), Kp * esz, ptr(hs), Kp * esz, ptr(perm), total, Kp * esz, self._stream()), "evo_gather_rows"))
+        up0, down0 = sp["experts"][0]
+        ys = torch.empty(max(total, 1), down0.Np, dtype=self.act_dtype, device=dev)
+        for e in range(E):
+            lo, ne = int(off[e]), int(cnt[e])
+            if ne == 0:
+                continue
+            up, down = sp["experts"][e]
+            z = self._linear(hs[lo:lo + ne], up, ne)
+            a = torch.empty(ne, down.Kp, dtype=self.act_dtype, device=dev)
+            self._record("glu_act", 3.0 * esz * ne * f.ff, lambda: check(lib.evo_glu_act(
+                ptr(z), C.c_void_p(z.data_ptr() + f.ff * esz), up.Np, ptr(a), down.Kp, ne, f.ff, 1, None, 0, 0, self._dt, self._stream()), "evo_glu_act"))
+            self._linear(a, down, ne, out=ys[lo:lo + ne])
+        # the always-on expert and the branch gate read every row
+        rest = sp["rest"]
+        zr = self._linear(h, rest, M)
+        base, ldb = None, 0
+        if f.shared_ff:
+            sd = sp["shared_down"]
+            a = torch.empty(M, sd.Kp, dtype=self.act_dtype, device=dev)
+            self._record("glu_act", 3.0 * esz * M * f.shared_ff, lambda: check(lib.evo_glu_act(
+                ptr(zr), C.c_void_p(zr.data_ptr() + f.shared_ff * esz), rest.Np, ptr(a), sd.Kp, M, f.shared_ff, 1, None, 0, 0, self._dt, self._stream()), "evo_glu_act"))
+            base = self._linear(a, sd, M)
+            ldb = sd.Np
+        ldo = _round_up(D, 64)
+        y = torch.empty(M, ldo, dtype=self.act_dtype, device=dev)
+        self._record("moe_combine", float(M) * D * esz * (2.0 + top), lambda: check(lib.evo_moe_combine(
+            ptr(ys), down0.Np, ptr(base), ldb, ptr(route), ptr(chosen), ptr(slot_of), ptr(y), ldo, M, D, E, top, self._dt, self._stream()), "evo_moe_combine"))
+        return _Pending(y, ldo, zr.data_ptr() + 2 * f.shared_ff * esz, rest.Np, w[f"l{i}.rg2.b"], self._packed["gain"][f"l{i}.norm2b"], hold=zr)
+
+    def _feed_forward(self, i, f, h, M, captured=False):
         pk = self._packed["layers"][i]
         dev, w, lib = h.device, self.weights, _lib.lib()
+        if f.kind == "moe" and not captured and M >= self.moe_sparse_min_rows and f.top < f.experts:
+            return self._experts_sparse(i, f, h, M)
         z = self._linear(h, pk["up"], M)
         esz, ld, F = z.element_size(), pk["up"].Np, pk["hidden"]
         a = torch.empty(M, pk["down"].Kp, dtype=self.act_dtype, device=dev)
@@ -279,7 +350,7 @@ class Movalorn(StreamDecoder):
                 pend = self._latent_attention(r, run.layer, m, h, B, L, ip, off, pos_dev)
             if layer.mlp is not None:
                 h = self._open(x, pend, gain[p + "norm2"], M)
-                pend = self._feed_forward(run.layer, layer.mlp, h, M)
+                pend = self._feed_forward(run.layer, layer.mlp, h, M, captured=pos_dev is not None)
             if self._tap is not None:
                 self._branch_norm(x, pend, 1.0)
                 pend = None

@@ -144,9 +144,10 @@ class StreamDecoder(KernelOps, nn.Module):
     def _dt(self) -> int:
         return 1 if self.act_dtype == torch.float32 else 0
 
-    def _linear(self, a, pk: _Packed, M: int):
-        """(M, Kp) activations -> (M, Np): rows of A are padded with zeros up to Kp by their producers."""
-        out = torch.empty(M, pk.Np, dtype=self.act_dtype, device=a.device)
+    def _linear(self, a, pk: _Packed, M: int, out=None):
+        """(M, Kp) activations -> (M, Np): rows of A are padded with zeros up to Kp by their producers.  out: rows of a (.., Np) buffer to fill."""
+        if out is None:
+            out = torch.empty(M, pk.Np, dtype=self.act_dtype, device=a.device)
         if self._dt or self.gemm_path == "simt":
             self._record(f"gemm_simt/{pk.N}x{pk.K}", 2.0 * M * pk.N * pk.K, lambda: check(_lib.lib().evo_gemm_simt(
                 ptr(a), pk.Kp, ptr(pk.w), pk.Kp, ptr(out), pk.Np, M, pk.N, pk.K, self._dt, self._stream()), "evo_gemm_simt"))

@@ -451,6 +451,16 @@ int evo_latent_attn_decode(const evo_latent_decode_params* p, void* workspace, s
  * weights (rows, E) fp32 = s * scale for the chosen experts, 0 for the others; chosen (rows, top) int32 (optional). */
 int evo_moe_route(const void* h, int64_t ldh, const void* router_w, const void* correction, float* weights, int32_t* chosen,
                   int64_t rows, int D, int E, int top, float scale, int dtype, void* stream);
+/* Sparse execution of the chosen experts.  chosen (n = rows * top) int32:
+ *   evo_moe_count    counts[e] += 1 per entry (counts zeroed by the caller);
+ *   evo_moe_scatter  slot_of[i] = offsets[chosen[i]] + running cursor (cursor zeroed by the caller), perm[slot] = i / top;
+ *   evo_gather_rows  dst row r = src row perm[r] (rows of width_bytes, all strides and bases multiples of 16 bytes);
+ *   evo_moe_combine  out[t] = base[t] + sum_k weights[t, chosen[t,k]] * ys[slot_of[t,k]]  (fp32 sums, base optional, pad columns zero). */
+int evo_moe_count(const int32_t* chosen, int64_t n, int E, int32_t* counts, void* stream);
+int evo_moe_scatter(const int32_t* chosen, int64_t n, int top, int E, const int32_t* offsets, int32_t* cursor, int32_t* perm, int32_t* slot_of, void* stream);
+int evo_gather_rows(const void* src, int64_t ld_src_bytes, void* dst, int64_t ld_dst_bytes, const int32_t* perm, int64_t rows, int64_t width_bytes, void* stream);
+int evo_moe_combine(const void* ys, int64_t ldy, const void* base, int64_t ldb, const float* weights, const int32_t* chosen, const int32_t* slot_of,
+                    void* out, int64_t ldo, int64_t rows, int D, int E, int top, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

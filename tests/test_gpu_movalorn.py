@@ -178,9 +178,9 @@ def test_mingru_whole_portions_and_steps(W, T, dtype):
     _close(state, S, 2e-5, "final state")
 
 
-@pytest.mark.parametrize("E,top,D", [(5, 2, 48), (16, 4, 100), (40, 1, 64), (3, 3, 33)])
-def test_router_scores_choice_and_weights(E, top, D):
-    M, scale = 9, 1.7
+@pytest.mark.parametrize("E,top,D,M", [(5, 2, 48, 9), (16, 4, 100, 1100), (40, 1, 64, 1030), (3, 3, 33, 9), (70, 6, 36, 17)])
+def test_router_scores_choice_and_weights(E, top, D, M):
+    scale = 1.7
     g = torch.Generator().manual_seed(E)
     h = torch.randn(M, D + 3, generator=g)
     rw, corr = _bf(torch.randn(E, D, generator=g) * 0.5), _bf(torch.randn(E, generator=g) * 0.4)
@@ -334,6 +334,11 @@ def test_model_whole_steps_and_portions_match_the_oracle_in_fp32(name):
     _close(_portions(model, tokens, [1] * T), want, 2e-5, f"{name}: token by token from the first token")
     _close(_portions(model, tokens, [40] + [1] * 35), want, 2e-5, f"{name}: prompt then steps")
     _close(_portions(model, tokens, [2, 2, 3, 30, 1, 2, 17, 9, 2, 5, 2]), want, 2e-5, f"{name}: portions")
+    model.moe_sparse_min_rows = 2                      # expert layers run only the chosen experts (the prompt path), steps stay dense
+    sparse, _ = model(torch.tensor([tokens], device=DEV))
+    _close(sparse[0], want, 2e-5, f"{name}: whole, sparse experts")
+    _close(_portions(model, tokens, [2, 2, 3, 30, 1, 2, 17, 9, 2, 5, 2]), want, 2e-5, f"{name}: portions, sparse experts")
+    model.moe_sparse_min_rows = 1024
     _close(_portions(model, tokens[:1], [1]), want[:1], 2e-5, f"{name}: a one-token sequence")
     _close(_portions(model, tokens[:2], [2]), want[:2], 2e-5, f"{name}: a two-token sequence")
 
@@ -367,6 +372,10 @@ def test_model_bf16_stays_within_rounding_of_the_oracle_and_of_itself():
     assert rel(whole[0], want) < 3e-2
     assert rel(cut, want) < 3e-2
     assert rel(cut, whole[0].cpu()) < 3e-2
+    model.moe_sparse_min_rows = 2
+    sparse, _ = model(torch.tensor([tokens], device=DEV))
+    assert rel(sparse[0], want) < 3e-2 and rel(sparse[0], whole[0].cpu()) < 3e-2
+    model.moe_sparse_min_rows = 1024
     model.gemm_path = "simt"                              # the tensor-core linear layers against the CUDA-core ones
     simt, _ = model(torch.tensor([tokens], device=DEV))
     assert rel(simt[0], whole[0].cpu()) < 2e-2
