@@ -5,9 +5,9 @@
 //                           pos * freq[i]), RMS-norms the latent (fp32) and appends [latent | 0.. | turned key part] to the cache.
 //   evo_latent_attn_decode  few query rows (the decoding step, short portions): the absorbed form, ql = Uk_h^T q_a, scores straight
 //                           against the cached latents, streaming softmax, the weighted sum of latents, then o = Uv_h . sum -- the
-//                           window's keys and values are never expanded, and every intermediate is fp32.  Three launches: absorb
+//                           window's keys and values are never expanded, and every intermediate is fp32.  Four launches: absorb
 //                           (Uk read once), a (key split, row, head group) kernel in which 8 or 16 heads share each tile of latents
-//                           through shared memory, and a merge that applies Uv and the head gate.  Shapes that path does not
+//                           through shared memory, a merge of the splits, and the Uv product with the head gate (Uv read once).  Shapes that path does not
 //                           cover run one CTA per (query, head) (latent_decode_kernel).
 // Prompts and long portions expand the visible rows of the cache with one GEMM against [Uk ; Uv] (the rotated part is carried into
 // every head's key by identity rows of that weight) and run the windowed attention kernel on the result.
@@ -195,15 +195,18 @@ __global__ void __launch_bounds__(DT) latent_decode_kernel(evo_latent_decode_par
 }
 
 // ---- few query rows, all heads of a group share every latent they read ------------------------------------------------------------
-// (1) absorb: ql[row, h] = [Uk_h^T q_a | q_b]  (fp32, rank + rot entries).  grid (H, rank / 128); the weights are read once per 8 rows.
+// (1) absorb: ql[row, h] = [Uk_h^T q_a | q_b]  (fp32, rank + rot entries).  grid (H, rank / 32); a CTA's 4 warps split the query
+// dimension, lanes are 32 adjacent latent entries (coalesced weight rows); the weights are read once per 8 rows.
 constexpr int AR = 8;         // rows per pass of the absorb kernel
 template <typename T>
 __global__ void __launch_bounds__(128) latent_absorb_kernel(evo_latent_decode_params p, float* __restrict__ ql) {
-  extern __shared__ float qs[];             // [AR][dim]
-  const int h = blockIdx.x, r = blockIdx.y * 128 + threadIdx.x;
+  extern __shared__ float qs[];             // [AR][dim], then [4][AR][32] partial sums
+  float* ps = qs + AR * p.dim;
+  const int h = blockIdx.x, lane = threadIdx.x & 31, dg = threadIdx.x >> 5, r = blockIdx.y * 32 + lane;
   const int hd = p.dim + p.rot, kw = p.rank + p.rot;
   const int64_t R = (int64_t)p.B * p.Lq;
   const bf16* uk = (const bf16*)p.uk + (int64_t)h * p.dim * p.rank;
+  const int d_per = (p.dim + 3) / 4, d0 = dg * d_per, d1 = min(p.dim, d0 + d_per);
   for (int64_t row0 = 0; row0 < R; row0 += AR) {
     const int nr = (int)min((int64_t)AR, R - row0);
     __syncthreads();
@@ -217,50 +220,70 @@ __global__ void __launch_bounds__(128) latent_absorb_kernel(evo_latent_decode_pa
         ql[((row0 + i) * p.H + h) * kw + p.rank + e] = ldf((const T*)p.q + (row0 + i) * p.ldq + (int64_t)h * hd + p.dim + e);
       }
     __syncthreads();
-    if (r < p.rank) {
-      float acc[AR];
+    float acc[AR];
 #pragma unroll
-      for (int i = 0; i < AR; ++i) acc[i] = 0.f;
-      for (int d = 0; d < p.dim; ++d) {
+    for (int i = 0; i < AR; ++i) acc[i] = 0.f;
+    if (r < p.rank) {
+#pragma unroll 4
+      for (int d = d0; d < d1; ++d) {
         const float w = __bfloat162float(uk[(int64_t)d * p.rank + r]);
 #pragma unroll
         for (int i = 0; i < AR; ++i) acc[i] = fmaf(qs[(i < nr ? i : 0) * p.dim + d], w, acc[i]);
       }
-      for (int i = 0; i < nr; ++i) ql[((row0 + i) * p.H + h) * kw + r] = acc[i];
+    }
+#pragma unroll
+    for (int i = 0; i < AR; ++i) ps[(dg * AR + i) * 32 + lane] = acc[i];
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nr * 32; idx += 128) {
+      const int i = idx >> 5, l = idx & 31;
+      if (blockIdx.y * 32 + l < p.rank)
+        ql[((row0 + i) * p.H + h) * kw + blockIdx.y * 32 + l] = ps[i * 32 + l] + ps[(AR + i) * 32 + l] + ps[(2 * AR + i) * 32 + l] + ps[(3 * AR + i) * 32 + l];
     }
   }
 }
 
-// (2) scores and value sums of one (key split, row, head group): tiles of KT = 256 / HG latents go through shared memory once for all HG heads;
-// thread (head, key) scores, thread (head, r0) accumulates the latent entries r0 + KT * k.  Partial (max, sum, acc) per split.
+// (2) scores and value sums of one (key split, row, head group): tiles of KT = 256 / HG latents go through shared memory once for all HG heads.
+// Rows in shared memory are [latent, padded to 4 | rotated part, padded to 4] with a row stride of 4 mod 32 floats, so that the 16-byte
+// reads of both phases are conflict-free: thread (head, key) scores its key with float4 dot products; thread (head, kk) accumulates the
+// latent entries 4 (kk + KT k) .. + 3.  One partial (max, sum, acc) per split.
 constexpr int SPLIT_T = 256;
 constexpr int RMAX = 32;      // latent entries per thread
+struct SplitLayout { int rp4, kwp, tw; };
+__host__ __device__ inline SplitLayout split_layout(int rank, int rot) {
+  SplitLayout l;
+  l.rp4 = (rank + 3) / 4 * 4;
+  l.kwp = l.rp4 + (rot + 3) / 4 * 4;
+  l.tw = l.kwp + (36 - l.kwp % 32) % 32;
+  return l;
+}
 template <typename T, int HG>
-__global__ void __launch_bounds__(SPLIT_T) latent_split_kernel(evo_latent_decode_params p, const float* __restrict__ ql, float* __restrict__ part, int n_split) {
+__global__ void __launch_bounds__(SPLIT_T) latent_split_kernel(evo_latent_decode_params p, const float* __restrict__ ql, float* __restrict__ part, int n_split, int pairs) {
   constexpr int KT = SPLIT_T / HG;          // keys per tile = threads per head (16 or 32: a head's threads sit in one warp)
-  extern __shared__ float sm[];
-  const int kw = p.rank + p.rot, tw = kw + 1;
-  float* qs = sm;                           // [HG][kw]
-  float* tile = qs + HG * kw;               // [KT][kw + 1]
+  extern __shared__ __align__(16) float sm[];
+  const SplitLayout lay = split_layout(p.rank, p.rot);
+  const int kw = p.rank + p.rot, kwp = lay.kwp, tw = lay.tw, rp4 = lay.rp4;
+  float* qs = sm;                           // [HG][kwp]
+  float* tile = qs + HG * kwp;              // [KT][tw]
   float* pb = tile + KT * tw;               // [HG][KT]
   const int split = blockIdx.x, hg = blockIdx.z;
   const int64_t row = blockIdx.y, b = row / p.Lq, rel = row % p.Lq;
   const int tid = threadIdx.x, hl = tid / KT, kk = tid % KT, w = tid >> 5, lane = tid & 31;
   const int h = hg * HG + hl;
-  const bool live = h < p.H;
   const int64_t i = (p.pos_dev ? (int64_t)*p.pos_dev : p.pos0) + rel;
   const int64_t lo = p.window > 0 ? max((int64_t)0, i - p.window + 1) : 0;
   const int64_t n = i - lo + 1;
   const int64_t tiles = (n + KT - 1) / KT, per = (tiles + n_split - 1) / n_split;
   const int64_t t_begin = split * per, t_end = min(tiles, t_begin + per);
+  for (int idx = tid; idx < HG * kwp + KT * tw; idx += SPLIT_T) sm[idx] = 0.f;       // pads stay zero
+  __syncthreads();
   for (int idx = tid; idx < HG * kw; idx += SPLIT_T) {
-    const int hh = hg * HG + idx / kw;
-    qs[idx] = hh < p.H ? ql[(row * p.H + hh) * kw + idx % kw] : 0.f;
+    const int hh = idx / kw, e = idx % kw;
+    if (hg * HG + hh < p.H) qs[hh * kwp + (e < p.rank ? e : rp4 + e - p.rank)] = ql[(row * p.H + hg * HG + hh) * kw + e];
   }
   const T* cb = (const T*)p.cache + b * p.cache_batch_stride;
-  float acc[RMAX];
+  float acc[RMAX / 4][4];
 #pragma unroll
-  for (int k = 0; k < RMAX; ++k) acc[k] = 0.f;
+  for (int k = 0; k < RMAX / 4; ++k) acc[k][0] = acc[k][1] = acc[k][2] = acc[k][3] = 0.f;
   float m_run = -INFINITY, l_run = 0.f;
   for (int64_t t = t_begin; t < t_end; ++t) {
     const int64_t k0 = lo + t * KT;
@@ -268,16 +291,32 @@ __global__ void __launch_bounds__(SPLIT_T) latent_split_kernel(evo_latent_decode
     __syncthreads();
     for (int key = w; key < nk; key += SPLIT_T / 32) {
       const T* c = cb + (k0 + key) * p.cache_row;
-      for (int e = lane; e < p.rank; e += 32) tile[key * tw + e] = ldf(c + e);
-      for (int e = lane; e < p.rot; e += 32) tile[key * tw + p.rank + e] = ldf(c + p.rank_pad + e);
+      float* dst = tile + key * tw;
+      if (pairs) {                          // even sizes and strides: two entries per load
+        for (int e = lane * 2; e < p.rank; e += 64) {
+          if (sizeof(T) == 2) { const uint32_t u = *reinterpret_cast<const uint32_t*>(c + e); dst[e] = bf_lo(u); dst[e + 1] = bf_hi(u); }
+          else { const float2 u = *reinterpret_cast<const float2*>(c + e); dst[e] = u.x; dst[e + 1] = u.y; }
+        }
+        for (int e = lane * 2; e < p.rot; e += 64) {
+          if (sizeof(T) == 2) { const uint32_t u = *reinterpret_cast<const uint32_t*>(c + p.rank_pad + e); dst[rp4 + e] = bf_lo(u); dst[rp4 + e + 1] = bf_hi(u); }
+          else { const float2 u = *reinterpret_cast<const float2*>(c + p.rank_pad + e); dst[rp4 + e] = u.x; dst[rp4 + e + 1] = u.y; }
+        }
+      } else {
+        for (int e = lane; e < p.rank; e += 32) dst[e] = ldf(c + e);
+        for (int e = lane; e < p.rot; e += 32) dst[rp4 + e] = ldf(c + p.rank_pad + e);
+      }
     }
     __syncthreads();
     float sc = -INFINITY;
     if (kk < nk) {
       float d = 0.f;
-      const float* qv = qs + hl * kw;
-      const float* cv = tile + kk * tw;
-      for (int e = 0; e < kw; ++e) d = fmaf(qv[e], cv[e], d);
+      const float4* qv = reinterpret_cast<const float4*>(qs + hl * kwp);
+      const float4* cv = reinterpret_cast<const float4*>(tile + kk * tw);
+#pragma unroll 4
+      for (int e = 0; e < kwp / 4; ++e) {
+        const float4 a = qv[e], c4 = cv[e];
+        d = fmaf(a.x, c4.x, fmaf(a.y, c4.y, fmaf(a.z, c4.z, fmaf(a.w, c4.w, d))));
+      }
       sc = d * p.scale;
     }
     float mx = sc;
@@ -294,29 +333,36 @@ __global__ void __launch_bounds__(SPLIT_T) latent_split_kernel(evo_latent_decode
     pb[hl * KT + kk] = pj;
     __syncwarp();                                       // a head's KT probabilities are written and read by lanes of one warp
 #pragma unroll
-    for (int k = 0; k < RMAX; ++k) acc[k] *= corr;
+    for (int k = 0; k < RMAX / 4; ++k) { acc[k][0] *= corr; acc[k][1] *= corr; acc[k][2] *= corr; acc[k][3] *= corr; }
     for (int key = 0; key < nk; ++key) {
       const float pk = pb[hl * KT + key];
-      const float* cv = tile + key * tw + kk;
+      const float4* cv = reinterpret_cast<const float4*>(tile + key * tw) + kk;
 #pragma unroll
-      for (int k = 0; k < RMAX; ++k)
-        if (kk + k * KT < p.rank) acc[k] = fmaf(pk, cv[k * KT], acc[k]);
+      for (int k = 0; k < RMAX / 4; ++k) {
+        if ((kk + k * KT) * 4 < rp4) {
+          const float4 c4 = cv[k * KT];
+          acc[k][0] = fmaf(pk, c4.x, acc[k][0]); acc[k][1] = fmaf(pk, c4.y, acc[k][1]);
+          acc[k][2] = fmaf(pk, c4.z, acc[k][2]); acc[k][3] = fmaf(pk, c4.w, acc[k][3]);
+        }
+      }
     }
   }
-  if (!live) return;
+  if (h >= p.H) return;
   float* dst = part + (((int64_t)split * gridDim.y + row) * p.H + h) * (p.rank + 2);
   if (kk == 0) { dst[0] = m_run; dst[1] = l_run; }
 #pragma unroll
-  for (int k = 0; k < RMAX; ++k)
-    if (kk + k * KT < p.rank) dst[2 + kk + k * KT] = acc[k];
+  for (int k = 0; k < RMAX / 4; ++k)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int r = (kk + k * KT) * 4 + j;
+      if (r < p.rank) dst[2 + r] = acc[k][j];
+    }
 }
 
-// (3) merge of the splits, o = Uv_h . (sum / l), head gate, store: one CTA per (row, head)
-template <typename T>
-__global__ void __launch_bounds__(256) latent_merge_kernel(evo_latent_decode_params p, const float* __restrict__ part, int n_split) {
-  extern __shared__ float ol[];             // [rank]
+// (3) merge of the splits: ol[row, h, :] = sum / l   (one CTA per (row, head); ol has the row stride of ql)
+__global__ void __launch_bounds__(128) latent_merge_kernel(evo_latent_decode_params p, const float* __restrict__ part, int n_split, float* __restrict__ ol) {
   const int64_t row = blockIdx.x;
-  const int h = blockIdx.y, tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
+  const int h = blockIdx.y, tid = threadIdx.x;
   const int64_t R = gridDim.x, stride = (int64_t)p.rank + 2;
   float mx = -INFINITY;
   for (int s = 0; s < n_split; ++s) mx = fmaxf(mx, part[(((int64_t)s * R + row) * p.H + h) * stride]);
@@ -326,27 +372,57 @@ __global__ void __launch_bounds__(256) latent_merge_kernel(evo_latent_decode_par
     if (src[0] != -INFINITY) l = fmaf(src[1], expf(src[0] - mx), l);
   }
   const float inv = 1.f / l;
-  for (int r = tid; r < p.rank; r += 256) {
+  float* dst = ol + (row * p.H + h) * (p.rank + p.rot);
+  for (int r = tid; r < p.rank; r += 128) {
     float t = 0.f;
     for (int s = 0; s < n_split; ++s) {
       const float* src = part + (((int64_t)s * R + row) * p.H + h) * stride;
       if (src[0] != -INFINITY) t = fmaf(src[2 + r], expf(src[0] - mx), t);
     }
-    ol[r] = t * inv;
+    dst[r] = t * inv;
   }
-  __syncthreads();
-  float gate = 1.f;
-  if (p.gate) gate = 1.f / (1.f + expf(-ldf((const T*)p.gate + row * p.ld_gate + h)));
+}
+
+// (4) o = Uv_h . ol, head gate, store: grid (H, vdim / 8), one value row of Uv per warp, read once for up to 16 query rows
+constexpr int UR = 16;        // query rows per pass
+template <typename T>
+__global__ void __launch_bounds__(256) latent_uv_kernel(evo_latent_decode_params p, const float* __restrict__ ol) {
+  extern __shared__ float os[];             // [UR][rank]
+  const int h = blockIdx.x, tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
+  const int kw = p.rank + p.rot;
+  const int64_t R = (int64_t)p.B * p.Lq;
   const bf16* uv = (const bf16*)p.uv + (int64_t)h * p.vdim * p.rank;
-  T* orow = (T*)p.out + row * p.ldo;
-  for (int v = w; v < p.vdim; v += 8) {
-    float d = 0.f;
-    for (int r = lane; r < p.rank; r += 32) d = fmaf(__bfloat162float(uv[(int64_t)v * p.rank + r]), ol[r], d);
-    d = warp_sum(d);
-    if (lane == 0) stf(orow + (int64_t)h * p.vdim + v, d * gate);
+  for (int64_t row0 = 0; row0 < R; row0 += UR) {
+    const int nr = (int)min((int64_t)UR, R - row0);
+    __syncthreads();
+    for (int idx = tid; idx < nr * p.rank; idx += 256) {
+      const int i = idx / p.rank, r = idx % p.rank;
+      os[i * p.rank + r] = ol[((row0 + i) * p.H + h) * kw + r];
+    }
+    __syncthreads();
+    for (int v = blockIdx.y * 8 + w; v < min(p.vdim, (int)(blockIdx.y + 1) * 8); v += 8) {
+      float d[UR];
+#pragma unroll
+      for (int i = 0; i < UR; ++i) d[i] = 0.f;
+      for (int r = lane; r < p.rank; r += 32) {
+        const float wv = __bfloat162float(uv[(int64_t)v * p.rank + r]);
+#pragma unroll
+        for (int i = 0; i < UR; ++i) d[i] = fmaf(wv, os[(i < nr ? i : 0) * p.rank + r], d[i]);
+      }
+#pragma unroll
+      for (int i = 0; i < UR; ++i) d[i] = warp_sum(d[i]);
+      if (lane == 0)
+        for (int i = 0; i < nr; ++i) {
+          const int64_t row = row0 + i;
+          float gate = 1.f;
+          if (p.gate) gate = 1.f / (1.f + expf(-ldf((const T*)p.gate + row * p.ld_gate + h)));
+          stf((T*)p.out + row * p.ldo + (int64_t)h * p.vdim + v, d[i] * gate);
+        }
+    }
+    if (h == p.H - 1 && blockIdx.y == 0)
+      for (int i = 0; i < nr; ++i)
+        for (int64_t c = (int64_t)p.H * p.vdim + tid; c < p.ldo; c += 256) stf((T*)p.out + (row0 + i) * p.ldo + c, 0.f);
   }
-  if (h == p.H - 1)
-    for (int64_t c = (int64_t)p.H * p.vdim + tid; c < p.ldo; c += 256) stf(orow + c, 0.f);
 }
 
 // plan of the shared-heads path: heads per group (0: not covered, the per-head kernel runs) and the number of key splits
@@ -357,7 +433,8 @@ inline SplitPlan split_plan(const evo_latent_decode_params* p) {
   else if (p->rank <= 32 * RMAX) pl.hg = 8;
   else return pl;
   const int kt = SPLIT_T / pl.hg, kw = p->rank + p->rot;
-  pl.smem = sizeof(float) * ((size_t)pl.hg * kw + (size_t)kt * (kw + 1) + SPLIT_T);
+  const SplitLayout lay = split_layout(p->rank, p->rot);
+  pl.smem = sizeof(float) * ((size_t)pl.hg * lay.kwp + (size_t)kt * lay.tw + SPLIT_T);
   if (pl.smem > 200 * 1024) { pl.hg = 0; return pl; }
   const int64_t R = (int64_t)p->B * p->Lq, groups = (p->H + pl.hg - 1) / pl.hg;
   const int64_t keys = p->max_keys > 0 ? (p->window > 0 ? std::min<int64_t>(p->window, p->max_keys) : p->max_keys) : (p->window > 0 ? p->window : 1024);
@@ -399,21 +476,28 @@ extern "C" int evo_latent_attn_decode(const evo_latent_decode_params* p, void* w
     const int kw = p->rank + p->rot;
     float* ql = (float*)workspace;
     float* part = ql + (size_t)R * p->H * kw;
-    const size_t sm_a = sizeof(float) * AR * p->dim;
-    dim3 ga((unsigned)p->H, (unsigned)((p->rank + 127) / 128));
+    const size_t sm_a = sizeof(float) * ((size_t)AR * p->dim + 4 * AR * 32);
+    dim3 ga((unsigned)p->H, (unsigned)((p->rank + 31) / 32));
     dim3 gs((unsigned)pl.n_split, (unsigned)R, (unsigned)((p->H + pl.hg - 1) / pl.hg));
     dim3 gm((unsigned)R, (unsigned)p->H);
-    const size_t sm_m = sizeof(float) * p->rank;
+    dim3 gu((unsigned)p->H, (unsigned)((p->vdim + 7) / 8));
+    const size_t sm_u = sizeof(float) * UR * p->rank;
+    EVO_REQUIRE(sm_u <= 200 * 1024, "evo_latent_attn_decode: latent too large");
+    const int esz = p->dtype ? 4 : 2;
+    const int pairs = p->rank % 2 == 0 && p->rot % 2 == 0 && p->rank_pad % 2 == 0 && p->cache_row % 2 == 0 && p->cache_batch_stride % 2 == 0 &&
+                      ((uintptr_t)p->cache & (uintptr_t)(2 * esz - 1)) == 0;
 #define EVO_LATENT_SPLIT(T)                                                                                                          \
     latent_absorb_kernel<T><<<ga, 128, sm_a, st>>>(*p, ql);                                                                          \
     if (pl.hg == 16) {                                                                                                               \
       if (pl.smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(latent_split_kernel<T, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem)); \
-      latent_split_kernel<T, 16><<<gs, SPLIT_T, pl.smem, st>>>(*p, ql, part, pl.n_split);                                           \
+      latent_split_kernel<T, 16><<<gs, SPLIT_T, pl.smem, st>>>(*p, ql, part, pl.n_split, pairs);                                    \
     } else {                                                                                                                         \
       if (pl.smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(latent_split_kernel<T, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));  \
-      latent_split_kernel<T, 8><<<gs, SPLIT_T, pl.smem, st>>>(*p, ql, part, pl.n_split);                                            \
+      latent_split_kernel<T, 8><<<gs, SPLIT_T, pl.smem, st>>>(*p, ql, part, pl.n_split, pairs);                                     \
     }                                                                                                                                \
-    latent_merge_kernel<T><<<gm, 256, sm_m, st>>>(*p, part, pl.n_split);
+    latent_merge_kernel<<<gm, 128, 0, st>>>(*p, part, pl.n_split, ql);                                                               \
+    if (sm_u > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(latent_uv_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_u));                \
+    latent_uv_kernel<T><<<gu, 256, sm_u, st>>>(*p, ql);
     if (p->dtype) { EVO_LATENT_SPLIT(float) } else { EVO_LATENT_SPLIT(bf16) }
 #undef EVO_LATENT_SPLIT
     return check_launch("evo_latent_attn_decode");

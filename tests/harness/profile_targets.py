@@ -60,4 +60,28 @@ elif what == "zaverax":
     for _ in range(2):
         model(ids)
     torch.cuda.synchronize()
+elif what in ("movalorn", "movalorn_step"):
+    # a 2-layer Movalorn model (minGRU + dense feed-forward, latent attention + experts) at width 2048: one prompt of 2 x 4096 tokens
+    # ("movalorn": every prompt kernel once per forward) or single-token steps of 16 sequences behind 2048 tokens ("movalorn_step")
+    from evo_b200.movalorn import Movalorn, MovalornConfig
+    gru = {"type": "mingru", "mixer": {"width": 2048}, "mlp": {"kind": "dense", "ff": 5632}}
+    lat = {"type": "latent_attention", "mixer": {"heads": 16, "dim": 64, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 0.088, "mask": {"size": 1024},
+                                                 "rot": {"base": 10000.0, "dims": 64}},
+           "mlp": {"kind": "moe", "expert": {"ff": 1408}, "router": {"experts": 16, "top": 4, "scale": 1.0}, "shared": {"ff": 1408}}}
+    mc = {"architecture": "Movalorn", "vocab": 512, "width": 2048, "norm": {"eps": 1e-5}, "logit_scale": 1.0, "layers": [gru, lat],
+          "embedding": {"scale": 1.0, "bigram": {"buckets": 4093, "mul_prev": 31, "mul_cur": 7}}}
+    model = Movalorn(MovalornConfig.from_dict(mc)).init_random(0, device=dev)
+    if what == "movalorn":
+        ids = torch.randint(0, 512, (2, 4096), device=dev)
+        for _ in range(2):
+            model(ids)
+    else:
+        B, ctx = 16, 2048
+        d = model.initialize_inference_params(max_seqlen=ctx + 64, max_batch_size=B)
+        lg, d = model(torch.randint(0, 512, (B, ctx), device=dev), inference_params_dict=d)
+        nxt = lg[:, -1].argmax(-1, keepdim=True)
+        for t in range(3):
+            d["mha"].seqlen_offset = d["hyena"].seqlen_offset = ctx + t
+            lg, _ = model(nxt, inference_params_dict=d)
+    torch.cuda.synchronize()
 print("done", what)
