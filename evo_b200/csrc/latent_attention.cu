@@ -439,7 +439,7 @@ inline SplitPlan split_plan(const evo_latent_decode_params* p) {
   const int64_t R = (int64_t)p->B * p->Lq, groups = (p->H + pl.hg - 1) / pl.hg;
   const int64_t keys = p->max_keys > 0 ? (p->window > 0 ? std::min<int64_t>(p->window, p->max_keys) : p->max_keys) : (p->window > 0 ? p->window : 1024);
   const int64_t tiles = (keys + kt - 1) / kt;
-  int64_t s = (2 * 148 + R * groups - 1) / (R * groups);
+  int64_t s = (3 * 148 + R * groups - 1) / (R * groups);          // three CTAs fit an SM (shared memory)
   s = std::max<int64_t>(1, std::min<int64_t>(s, (tiles + 1) / 2));
   pl.n_split = (int)std::min<int64_t>(s, 64);
   pl.ws = sizeof(float) * ((size_t)R * p->H * kw + (size_t)pl.n_split * R * p->H * (p->rank + 2));

@@ -216,10 +216,9 @@ class Movalorn(StreamDecoder):
             lo = max(0, off - (m.window - 1)) if m.window > 0 else 0
             n = off + L - lo
             ex = pk["expand"]
-            if B == 1:
-                kv = self._linear(cache[0, lo:off + L], ex, n)
-            else:
-                kv = torch.stack([self._linear(cache[b, lo:off + L], ex, n) for b in range(B)])
+            kv = torch.empty(B, n, ex.Np, dtype=self.act_dtype, device=dev)
+            for b in range(B):
+                self._linear(cache[b, lo:off + L], ex, n, out=kv[b])
             ap = WindowAttnParams(q=z.data_ptr(), q_tok_stride=ld, gate=gate_ptr, gate_tok_stride=ld, gate_per_head=1,
                                   k=kv.data_ptr() - lo * ex.Np * esz, v=kv.data_ptr() + (qw - lo * ex.Np) * esz,
                                   k_tok_stride=ex.Np, v_tok_stride=ex.Np, k_batch_stride=n * ex.Np, v_batch_stride=n * ex.Np,
