@@ -12,6 +12,7 @@
 // Prompts and long portions expand the visible rows of the cache with one GEMM against [Uk ; Uv] (the rotated part is carried into
 // every head's key by identity rows of that weight) and run the windowed attention kernel on the result.
 #include "common.cuh"
+#include "mma_sync.cuh"
 #include "../../include/evo_b200.h"
 #include <math.h>
 #include <stdlib.h>
@@ -359,6 +360,149 @@ __global__ void __launch_bounds__(SPLIT_T) latent_split_kernel(evo_latent_decode
     }
 }
 
+// (2b) the same partial on the tensor cores, for bf16 caches, groups of 16 heads and latents of 64 / 128 / 256 / 512 entries: the 16 heads are
+// the M dimension of mma.sync.m16n8k16.  q_l enters as a bf16 high part plus a bf16 remainder (two MMAs; products with the bf16 latents are
+// exact, sums fp32), the scores of a 64-key tile go through shared memory in fp32, every warp rebuilds the tile's softmax weights in
+// fragment layout (fp32), and the weights enter the value sum as high + remainder against the SAME tile (read transposed by ldmatrix).
+// The four warps split the keys for the scores and the latent columns for the values.  NV8 = rank / 32 (8-column tiles per warp).
+constexpr int MK = 64;        // keys per tile
+template <int NV8>
+__global__ void __launch_bounds__(128) latent_split_mma_kernel(evo_latent_decode_params p, const float* __restrict__ ql, float* __restrict__ part, int n_split) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  const int kw = p.rank + p.rot, st = kw + 8;             // row stride in bf16: 16 bytes of padding, conflict-free fragment reads
+  bf16* Qh = reinterpret_cast<bf16*>(smraw);              // [16][st] high parts of [q_l | q_b]
+  bf16* Ql = Qh + 16 * st;                                // [16][st] remainders
+  bf16* Ks = Ql + 16 * st;                                // [MK][st] latents and rotated key parts of the tile
+  float* Ss = reinterpret_cast<float*>(Ks + MK * st);     // [16][MK + 2] scores (base-2 exponent units)
+  constexpr int sst = MK + 2;
+  const int split = blockIdx.x, hg = blockIdx.z;
+  const int64_t row = blockIdx.y, b = row / p.Lq, rel = row % p.Lq;
+  const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, qr = lane >> 2, qc = (lane & 3) * 2;
+  const int64_t i = (p.pos_dev ? (int64_t)*p.pos_dev : p.pos0) + rel;
+  const int64_t lo = p.window > 0 ? max((int64_t)0, i - p.window + 1) : 0;
+  const int64_t n = i - lo + 1;
+  const int64_t tiles = (n + MK - 1) / MK, per = (tiles + n_split - 1) / n_split;
+  const int64_t t_begin = split * per, t_end = min(tiles, t_begin + per);
+  for (int hh = w; hh < 16; hh += 4) {                     // a warp per head row: coalesced, no index division
+    const int h = hg * 16 + hh;
+    const float* src = ql + (row * p.H + (h < p.H ? h : 0)) * kw;
+#pragma unroll 4
+    for (int e = lane; e < kw; e += 32) {
+      const float v = h < p.H ? src[e] : 0.f;
+      const bf16 hi = __float2bfloat16_rn(v);
+      Qh[hh * st + e] = hi;
+      Ql[hh * st + e] = __float2bfloat16_rn(v - __bfloat162float(hi));
+    }
+  }
+  const bf16* cb = (const bf16*)p.cache + b * p.cache_batch_stride;
+  float O[NV8][4];
+#pragma unroll
+  for (int nn = 0; nn < NV8; ++nn) O[nn][0] = O[nn][1] = O[nn][2] = O[nn][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;      // rows qr and qr + 8 (the same in every warp)
+  const float scale2 = p.scale * 1.4426950408889634f;
+  const int c16 = kw / 8;                                        // 16-byte chunks per row
+  for (int64_t t = t_begin; t < t_end; ++t) {
+    const int64_t k0 = lo + t * MK;
+    const int nk = (int)min((int64_t)MK, i + 1 - k0);
+    __syncthreads();
+    for (int r = w; r < MK; r += 4) {                       // a warp per key row, 16 bytes per lane
+      const bf16* src = cb + (k0 + (r < nk ? r : 0)) * p.cache_row;
+#pragma unroll 3
+      for (int c = lane; c < c16; c += 32) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < nk) v = *reinterpret_cast<const uint4*>(src + c * 8);
+        *reinterpret_cast<uint4*>(Ks + r * st + c * 8) = v;
+      }
+    }
+    __syncthreads();
+    // scores of keys [16 w, 16 w + 16): S = (Qh + Ql) . K^T
+    float S[2][4];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) S[u][0] = S[u][1] = S[u][2] = S[u][3] = 0.f;
+    for (int ks = 0; ks < kw / 16; ++ks) {
+      uint32_t ah[4], al[4], kf[4];
+      const bf16* qa = Qh + ks * 16 + qc;
+      ah[0] = *reinterpret_cast<const uint32_t*>(qa + qr * st);
+      ah[1] = *reinterpret_cast<const uint32_t*>(qa + (qr + 8) * st);
+      ah[2] = *reinterpret_cast<const uint32_t*>(qa + qr * st + 8);
+      ah[3] = *reinterpret_cast<const uint32_t*>(qa + (qr + 8) * st + 8);
+      const bf16* qb = Ql + ks * 16 + qc;
+      al[0] = *reinterpret_cast<const uint32_t*>(qb + qr * st);
+      al[1] = *reinterpret_cast<const uint32_t*>(qb + (qr + 8) * st);
+      al[2] = *reinterpret_cast<const uint32_t*>(qb + qr * st + 8);
+      al[3] = *reinterpret_cast<const uint32_t*>(qb + (qr + 8) * st + 8);
+      ldmatrix_x4(kf, Ks + ((2 * w + (lane >> 4)) * 8 + (lane & 7)) * st + ks * 16 + ((lane >> 3) & 1) * 8);
+      mma_bf16(S[0], ah, kf[0], kf[1]); mma_bf16(S[0], al, kf[0], kf[1]);
+      mma_bf16(S[1], ah, kf[2], kf[3]); mma_bf16(S[1], al, kf[2], kf[3]);
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int col = (2 * w + u) * 8 + qc;
+      Ss[qr * sst + col] = col < nk ? S[u][0] * scale2 : -INFINITY;
+      Ss[qr * sst + col + 1] = col + 1 < nk ? S[u][1] * scale2 : -INFINITY;
+      Ss[(qr + 8) * sst + col] = col < nk ? S[u][2] * scale2 : -INFINITY;
+      Ss[(qr + 8) * sst + col + 1] = col + 1 < nk ? S[u][3] * scale2 : -INFINITY;
+    }
+    __syncthreads();
+    // the tile's weights in A-fragment layout: P[kk] = rows (qr, qr + 8) x keys 16 kk + qc + {0, 1, 8, 9}
+    float P[MK / 16][8];
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int kk = 0; kk < MK / 16; ++kk) {
+      const float2 a0 = *reinterpret_cast<const float2*>(Ss + qr * sst + kk * 16 + qc), a1 = *reinterpret_cast<const float2*>(Ss + qr * sst + kk * 16 + 8 + qc);
+      const float2 b0 = *reinterpret_cast<const float2*>(Ss + (qr + 8) * sst + kk * 16 + qc), b1 = *reinterpret_cast<const float2*>(Ss + (qr + 8) * sst + kk * 16 + 8 + qc);
+      P[kk][0] = a0.x; P[kk][1] = a0.y; P[kk][2] = b0.x; P[kk][3] = b0.y; P[kk][4] = a1.x; P[kk][5] = a1.y; P[kk][6] = b1.x; P[kk][7] = b1.y;
+      mx0 = fmaxf(mx0, fmaxf(fmaxf(a0.x, a0.y), fmaxf(a1.x, a1.y)));
+      mx1 = fmaxf(mx1, fmaxf(fmaxf(b0.x, b0.y), fmaxf(b1.x, b1.y)));
+    }
+    mx0 = quad_max(mx0); mx1 = quad_max(mx1);
+    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);          // finite: every tile of the range has a visible key
+    const float c0 = ex2(m0 - n0), c1 = ex2(m1 - n1);
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < MK / 16; ++kk) {
+      P[kk][0] = ex2(P[kk][0] - n0); P[kk][1] = ex2(P[kk][1] - n0); P[kk][4] = ex2(P[kk][4] - n0); P[kk][5] = ex2(P[kk][5] - n0);
+      P[kk][2] = ex2(P[kk][2] - n1); P[kk][3] = ex2(P[kk][3] - n1); P[kk][6] = ex2(P[kk][6] - n1); P[kk][7] = ex2(P[kk][7] - n1);
+      s0 += P[kk][0] + P[kk][1] + P[kk][4] + P[kk][5];
+      s1 += P[kk][2] + P[kk][3] + P[kk][6] + P[kk][7];
+    }
+    l0 = l0 * c0 + quad_sum(s0); l1 = l1 * c1 + quad_sum(s1);
+    m0 = n0; m1 = n1;
+#pragma unroll
+    for (int nn = 0; nn < NV8; ++nn) { O[nn][0] *= c0; O[nn][1] *= c0; O[nn][2] *= c1; O[nn][3] *= c1; }
+    // O[:, columns of this warp] += P . C
+#pragma unroll
+    for (int kk = 0; kk < MK / 16; ++kk) {
+      uint32_t ah[4], al[4];
+      split_pack(P[kk][0], P[kk][1], ah[0], al[0]);
+      split_pack(P[kk][2], P[kk][3], ah[1], al[1]);
+      split_pack(P[kk][4], P[kk][5], ah[2], al[2]);
+      split_pack(P[kk][6], P[kk][7], ah[3], al[3]);
+#pragma unroll
+      for (int nn = 0; nn < NV8; nn += 2) {
+        uint32_t bv[4];
+        ldmatrix_x4_trans(bv, Ks + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * st + (w * NV8 + nn + (lane >> 4)) * 8);
+        mma_bf16(O[nn], ah, bv[0], bv[1]); mma_bf16(O[nn], al, bv[0], bv[1]);
+        mma_bf16(O[nn + 1], ah, bv[2], bv[3]); mma_bf16(O[nn + 1], al, bv[2], bv[3]);
+      }
+    }
+  }
+  // partials in natural-exponent units, as the merge kernel expects
+  const float ln2 = 0.6931471805599453f;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int h = hg * 16 + qr + 8 * half;
+    if (h >= p.H) continue;
+    float* dst = part + (((int64_t)split * gridDim.y + row) * p.H + h) * (p.rank + 2);
+    if (w == 0 && qc == 0) { dst[0] = (half ? m1 : m0) * ln2; dst[1] = half ? l1 : l0; }
+#pragma unroll
+    for (int nn = 0; nn < NV8; ++nn) {
+      const int r = (w * NV8 + nn) * 8 + qc;
+      dst[2 + r] = O[nn][2 * half]; dst[2 + r + 1] = O[nn][2 * half + 1];
+    }
+  }
+}
+
 // (3) merge of the splits: ol[row, h, :] = sum / l   (one CTA per (row, head); ol has the row stride of ql)
 __global__ void __launch_bounds__(128) latent_merge_kernel(evo_latent_decode_params p, const float* __restrict__ part, int n_split, float* __restrict__ ol) {
   const int64_t row = blockIdx.x;
@@ -426,21 +570,28 @@ __global__ void __launch_bounds__(256) latent_uv_kernel(evo_latent_decode_params
 }
 
 // plan of the shared-heads path: heads per group (0: not covered, the per-head kernel runs) and the number of key splits
-struct SplitPlan { int hg, n_split; size_t smem, ws; };
+struct SplitPlan { int hg, n_split, mma; size_t smem, ws; };
 inline SplitPlan split_plan(const evo_latent_decode_params* p) {
-  SplitPlan pl = {0, 1, 0, 0};
+  SplitPlan pl = {0, 1, 0, 0, 0};
   if (p->H >= 12 && p->rank <= 16 * RMAX) pl.hg = 16;
   else if (p->rank <= 32 * RMAX) pl.hg = 8;
   else return pl;
-  const int kt = SPLIT_T / pl.hg, kw = p->rank + p->rot;
+  int kt = SPLIT_T / pl.hg;
+  const int kw = p->rank + p->rot;
   const SplitLayout lay = split_layout(p->rank, p->rot);
   pl.smem = sizeof(float) * ((size_t)pl.hg * lay.kwp + (size_t)kt * lay.tw + SPLIT_T);
+  // tensor-core form: bf16 cache rows that are [latent | rotated part] without padding in between, 16-byte chunks
+  const size_t smem_mma = sizeof(bf16) * (size_t)(32 + MK) * (kw + 8) + sizeof(float) * 16 * (MK + 2);
+  if (p->dtype == 0 && pl.hg == 16 && (p->rank == 64 || p->rank == 128 || p->rank == 256 || p->rank == 512) && p->rot % 16 == 0 && p->rank_pad == p->rank &&
+      p->cache_row % 8 == 0 && p->cache_batch_stride % 8 == 0 && ((uintptr_t)p->cache & 15) == 0 && smem_mma <= 200 * 1024) {
+    pl.mma = 1; pl.smem = smem_mma; kt = MK;
+  }
   if (pl.smem > 200 * 1024) { pl.hg = 0; return pl; }
   const int64_t R = (int64_t)p->B * p->Lq, groups = (p->H + pl.hg - 1) / pl.hg;
   const int64_t keys = p->max_keys > 0 ? (p->window > 0 ? std::min<int64_t>(p->window, p->max_keys) : p->max_keys) : (p->window > 0 ? p->window : 1024);
   const int64_t tiles = (keys + kt - 1) / kt;
-  int64_t s = (3 * 148 + R * groups - 1) / (R * groups);          // three CTAs fit an SM (shared memory)
-  s = std::max<int64_t>(1, std::min<int64_t>(s, (tiles + 1) / 2));
+  int64_t s = ((pl.mma ? 2 : 3) * 148 + R * groups - 1) / (R * groups);          // CTAs that fit the GPU at once (shared memory)
+  s = std::max<int64_t>(1, std::min<int64_t>(s, pl.mma ? tiles : (tiles + 1) / 2));
   pl.n_split = (int)std::min<int64_t>(s, 64);
   pl.ws = sizeof(float) * ((size_t)R * p->H * kw + (size_t)pl.n_split * R * p->H * (p->rank + 2));
   return pl;
@@ -498,7 +649,22 @@ extern "C" int evo_latent_attn_decode(const evo_latent_decode_params* p, void* w
     latent_merge_kernel<<<gm, 128, 0, st>>>(*p, part, pl.n_split, ql);                                                               \
     if (sm_u > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(latent_uv_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_u));                \
     latent_uv_kernel<T><<<gu, 256, sm_u, st>>>(*p, ql);
-    if (p->dtype) { EVO_LATENT_SPLIT(float) } else { EVO_LATENT_SPLIT(bf16) }
+#define EVO_LATENT_MMA(NV8)                                                                                                          \
+    { if (pl.smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(latent_split_mma_kernel<NV8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem)); \
+      latent_split_mma_kernel<NV8><<<gs, 128, pl.smem, st>>>(*p, ql, part, pl.n_split); }
+    if (pl.mma) {
+      latent_absorb_kernel<bf16><<<ga, 128, sm_a, st>>>(*p, ql);
+      switch (p->rank) {
+        case 64: EVO_LATENT_MMA(2) break;
+        case 128: EVO_LATENT_MMA(4) break;
+        case 256: EVO_LATENT_MMA(8) break;
+        default: EVO_LATENT_MMA(16) break;
+      }
+      latent_merge_kernel<<<gm, 128, 0, st>>>(*p, part, pl.n_split, ql);
+      if (sm_u > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(latent_uv_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_u));
+      latent_uv_kernel<bf16><<<gu, 256, sm_u, st>>>(*p, ql);
+    } else if (p->dtype) { EVO_LATENT_SPLIT(float) } else { EVO_LATENT_SPLIT(bf16) }
+#undef EVO_LATENT_MMA
 #undef EVO_LATENT_SPLIT
     return check_launch("evo_latent_attn_decode");
   }

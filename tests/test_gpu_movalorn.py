@@ -255,6 +255,40 @@ def test_latent_attention_mixer_matches_the_oracle(mode, H, dim, rd, vd, rank, w
     _close(got, want, 2e-5, f"{mode}")
 
 
+@pytest.mark.parametrize("H,dim,rd,vd,rank,window,B", [(16, 16, 16, 24, 64, 150, 1), (13, 8, 32, 8, 128, 70, 3), (20, 8, 16, 16, 256, 300, 2)])
+def test_latent_attention_steps_on_tensor_cores(H, dim, rd, vd, rank, window, B):
+    """bf16 activations, groups of 16 heads, latents of 64 / 128 / 256 entries: the step attention runs its scores and value sums on the
+    tensor cores.  Same inputs through the per-(query, head) kernel (fp32 arithmetic throughout) must agree to the output's bf16 rounding,
+    and both with the oracle to bf16 accuracy; steps start inside the first tile, cross tile borders and run past the window."""
+    cfg = O.make_config(layers=("latent_attention",), heads=H, dim=dim, rot_dim=rd, vdim=vd, kv_rank=rank, window=window, width=64)
+    W = O.random_weights(cfg, seed=rank)
+    model = _model(cfg, W, B16)
+    model._ensure_packed()
+    T0, steps = 40, 2 * window // 3 + 70
+    T = T0 + steps
+    h = _bf(torch.randn(B, T, 64, generator=torch.Generator().manual_seed(4)))
+    m = cfg["layers"][0]["mixer"]
+    rows = sorted(set(list(range(T0, T, 23)) + [T0, T0 + 1, 63, 64, 65, 127, 128, window - 1, window, window + 1, T - 1]) & set(range(T0, T)))
+    want = O.latent_attention(h[0].double(), {k: v.double() for k, v in W.items()}, "l0.mix.", m, cfg["norm"]["eps"], [], rows=rows)[rows]
+    hd = h.to(DEV)
+    mc = model.config.layers[0].mixer
+    outs = {}
+    for path in ("shared", "head"):
+        model.latent_decode_path = path
+        state = model.initialize_inference_params(max_seqlen=T + 5, max_batch_size=B)
+        got = []
+        with torch.no_grad():
+            model._latent_attention(0, 0, mc, hd[:, :T0].reshape(B * T0, 64).contiguous(), B, T0, state["mha"], 0, None)
+            for t in range(T0, T):
+                pend = model._latent_attention(0, 0, mc, hd[:, t].contiguous(), B, 1, state["mha"], t, None)
+                got.append(pend.y[:, :64].float().clone())
+        outs[path] = torch.stack(got, 1)                      # (B, steps, 64)
+    _close(outs["shared"], outs["head"], 1.2e-2, "tensor-core steps against the fp32 per-head kernel")
+    idx = [r - T0 for r in rows]
+    _close(outs["shared"][0, idx], want, 2.5e-2, "tensor-core steps against the oracle")
+    _close(outs["head"][0, idx], want, 2.5e-2, "per-head steps against the oracle")
+
+
 def _dominant_token_weights(cfg, W, plain, odd):
     """Weights under which the key of the token `odd` (after `plain`) beats a plain key by 10 in every head, whatever the distance:
     the rotated query rows are zeroed (scores no longer depend on the position) and every head's unrotated query rows are scaled."""
