@@ -199,8 +199,14 @@ __global__ void __launch_bounds__(DT) latent_decode_kernel(evo_latent_decode_par
 // (1) absorb: ql[row, h] = [Uk_h^T q_a | q_b]  (fp32, rank + rot entries).  grid (H, rank / 32); a CTA's 4 warps split the query
 // dimension, lanes are 32 adjacent latent entries (coalesced weight rows); the weights are read once per 8 rows.
 constexpr int AR = 8;         // rows per pass of the absorb kernel
+// bf16 high part and bf16 remainder of v at entry e of a [2][kw] row (the tensor-core step kernel reads both with 16-byte copies)
+__device__ __forceinline__ void put_split(bf16* row, int kw, int e, float v) {
+  const bf16 hi = __float2bfloat16_rn(v);
+  row[e] = hi;
+  row[kw + e] = __float2bfloat16_rn(v - __bfloat162float(hi));
+}
 template <typename T>
-__global__ void __launch_bounds__(128) latent_absorb_kernel(evo_latent_decode_params p, float* __restrict__ ql) {
+__global__ void __launch_bounds__(128) latent_absorb_kernel(evo_latent_decode_params p, float* __restrict__ ql, bf16* __restrict__ qsplit) {
   extern __shared__ float qs[];             // [AR][dim], then [4][AR][32] partial sums
   float* ps = qs + AR * p.dim;
   const int h = blockIdx.x, lane = threadIdx.x & 31, dg = threadIdx.x >> 5, r = blockIdx.y * 32 + lane;
@@ -218,7 +224,9 @@ __global__ void __launch_bounds__(128) latent_absorb_kernel(evo_latent_decode_pa
     if (blockIdx.y == 0)
       for (int idx = threadIdx.x; idx < nr * p.rot; idx += 128) {
         const int i = idx / p.rot, e = idx % p.rot;
-        ql[((row0 + i) * p.H + h) * kw + p.rank + e] = ldf((const T*)p.q + (row0 + i) * p.ldq + (int64_t)h * hd + p.dim + e);
+        const float v = ldf((const T*)p.q + (row0 + i) * p.ldq + (int64_t)h * hd + p.dim + e);
+        ql[((row0 + i) * p.H + h) * kw + p.rank + e] = v;
+        if (qsplit) put_split(qsplit + ((row0 + i) * p.H + h) * 2 * kw, kw, p.rank + e, v);
       }
     __syncthreads();
     float acc[AR];
@@ -237,8 +245,11 @@ __global__ void __launch_bounds__(128) latent_absorb_kernel(evo_latent_decode_pa
     __syncthreads();
     for (int idx = threadIdx.x; idx < nr * 32; idx += 128) {
       const int i = idx >> 5, l = idx & 31;
-      if (blockIdx.y * 32 + l < p.rank)
-        ql[((row0 + i) * p.H + h) * kw + blockIdx.y * 32 + l] = ps[i * 32 + l] + ps[(AR + i) * 32 + l] + ps[(2 * AR + i) * 32 + l] + ps[(3 * AR + i) * 32 + l];
+      if (blockIdx.y * 32 + l < p.rank) {
+        const float v = ps[i * 32 + l] + ps[(AR + i) * 32 + l] + ps[(2 * AR + i) * 32 + l] + ps[(3 * AR + i) * 32 + l];
+        ql[((row0 + i) * p.H + h) * kw + blockIdx.y * 32 + l] = v;
+        if (qsplit) put_split(qsplit + ((row0 + i) * p.H + h) * 2 * kw, kw, blockIdx.y * 32 + l, v);
+      }
     }
   }
 }
@@ -366,8 +377,15 @@ __global__ void __launch_bounds__(SPLIT_T) latent_split_kernel(evo_latent_decode
 // fragment layout (fp32), and the weights enter the value sum as high + remainder against the SAME tile (read transposed by ldmatrix).
 // The four warps split the keys for the scores and the latent columns for the values.  NV8 = rank / 32 (8-column tiles per warp).
 constexpr int MK = 64;        // keys per tile
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* src, int src_bytes) {      // src_bytes 0: zero fill
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(smem_u32(smem_dst)), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
 template <int NV8>
-__global__ void __launch_bounds__(128) latent_split_mma_kernel(evo_latent_decode_params p, const float* __restrict__ ql, float* __restrict__ part, int n_split) {
+__global__ void __launch_bounds__(128) latent_split_mma_kernel(evo_latent_decode_params p, const bf16* __restrict__ qsplit, float* __restrict__ part, int n_split) {
   extern __shared__ __align__(16) unsigned char smraw[];
   const int kw = p.rank + p.rot, st = kw + 8;             // row stride in bf16: 16 bytes of padding, conflict-free fragment reads
   bf16* Qh = reinterpret_cast<bf16*>(smraw);              // [16][st] high parts of [q_l | q_b]
@@ -383,16 +401,13 @@ __global__ void __launch_bounds__(128) latent_split_mma_kernel(evo_latent_decode
   const int64_t n = i - lo + 1;
   const int64_t tiles = (n + MK - 1) / MK, per = (tiles + n_split - 1) / n_split;
   const int64_t t_begin = split * per, t_end = min(tiles, t_begin + per);
-  for (int hh = w; hh < 16; hh += 4) {                     // a warp per head row: coalesced, no index division
-    const int h = hg * 16 + hh;
-    const float* src = ql + (row * p.H + (h < p.H ? h : 0)) * kw;
-#pragma unroll 4
-    for (int e = lane; e < kw; e += 32) {
-      const float v = h < p.H ? src[e] : 0.f;
-      const bf16 hi = __float2bfloat16_rn(v);
-      Qh[hh * st + e] = hi;
-      Ql[hh * st + e] = __float2bfloat16_rn(v - __bfloat162float(hi));
-    }
+  const int c16 = kw / 8;                                        // 16-byte chunks per row
+  // both query parts of the 16 heads: asynchronous 16-byte copies (zero-filled past the last head), in flight together with the first tile
+  for (int rr = w; rr < 32; rr += 4) {
+    const int hh = rr & 15, part_ = rr >> 4, h = hg * 16 + hh;
+    const bf16* src = qsplit + ((row * p.H + (h < p.H ? h : 0)) * 2 + part_) * kw;
+    bf16* dst = (part_ ? Ql : Qh) + hh * st;
+    for (int c = lane; c < c16; c += 32) cp_async16(dst + c * 8, src + c * 8, h < p.H ? 16 : 0);
   }
   const bf16* cb = (const bf16*)p.cache + b * p.cache_batch_stride;
   float O[NV8][4];
@@ -400,20 +415,15 @@ __global__ void __launch_bounds__(128) latent_split_mma_kernel(evo_latent_decode
   for (int nn = 0; nn < NV8; ++nn) O[nn][0] = O[nn][1] = O[nn][2] = O[nn][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;      // rows qr and qr + 8 (the same in every warp)
   const float scale2 = p.scale * 1.4426950408889634f;
-  const int c16 = kw / 8;                                        // 16-byte chunks per row
   for (int64_t t = t_begin; t < t_end; ++t) {
     const int64_t k0 = lo + t * MK;
     const int nk = (int)min((int64_t)MK, i + 1 - k0);
     __syncthreads();
-    for (int r = w; r < MK; r += 4) {                       // a warp per key row, 16 bytes per lane
+    for (int r = w; r < MK; r += 4) {                       // a warp per key row, 16 bytes per lane, zero-filled past the last key
       const bf16* src = cb + (k0 + (r < nk ? r : 0)) * p.cache_row;
-#pragma unroll 3
-      for (int c = lane; c < c16; c += 32) {
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (r < nk) v = *reinterpret_cast<const uint4*>(src + c * 8);
-        *reinterpret_cast<uint4*>(Ks + r * st + c * 8) = v;
-      }
+      for (int c = lane; c < c16; c += 32) cp_async16(Ks + r * st + c * 8, src + c * 8, r < nk ? 16 : 0);
     }
+    cp_async_wait_all();
     __syncthreads();
     // scores of keys [16 w, 16 w + 16): S = (Qh + Ql) . K^T
     float S[2][4];
@@ -487,6 +497,7 @@ __global__ void __launch_bounds__(128) latent_split_mma_kernel(evo_latent_decode
       }
     }
   }
+  cp_async_wait_all();                                           // a split without tiles still has its query copies in flight
   // partials in natural-exponent units, as the merge kernel expects
   const float ln2 = 0.6931471805599453f;
 #pragma unroll
@@ -590,10 +601,11 @@ inline SplitPlan split_plan(const evo_latent_decode_params* p) {
   const int64_t R = (int64_t)p->B * p->Lq, groups = (p->H + pl.hg - 1) / pl.hg;
   const int64_t keys = p->max_keys > 0 ? (p->window > 0 ? std::min<int64_t>(p->window, p->max_keys) : p->max_keys) : (p->window > 0 ? p->window : 1024);
   const int64_t tiles = (keys + kt - 1) / kt;
-  int64_t s = ((pl.mma ? 2 : 3) * 148 + R * groups - 1) / (R * groups);          // CTAs that fit the GPU at once (shared memory)
+  int64_t s = ((pl.mma ? 1 : 3) * 148 + R * groups - 1) / (R * groups);          // CTAs that fit the GPU at once (shared memory)
   s = std::max<int64_t>(1, std::min<int64_t>(s, pl.mma ? tiles : (tiles + 1) / 2));
   pl.n_split = (int)std::min<int64_t>(s, 64);
-  pl.ws = sizeof(float) * ((size_t)R * p->H * kw + (size_t)pl.n_split * R * p->H * (p->rank + 2));
+  pl.ws = sizeof(float) * (((size_t)R * p->H * kw + (size_t)pl.n_split * R * p->H * (p->rank + 2) + 3) / 4 * 4);
+  if (pl.mma) pl.ws += sizeof(bf16) * 2 * (size_t)R * p->H * kw;          // the absorbed queries as bf16 high parts and remainders
   return pl;
 }
 
@@ -638,7 +650,7 @@ extern "C" int evo_latent_attn_decode(const evo_latent_decode_params* p, void* w
     const int pairs = p->rank % 2 == 0 && p->rot % 2 == 0 && p->rank_pad % 2 == 0 && p->cache_row % 2 == 0 && p->cache_batch_stride % 2 == 0 &&
                       ((uintptr_t)p->cache & (uintptr_t)(2 * esz - 1)) == 0;
 #define EVO_LATENT_SPLIT(T)                                                                                                          \
-    latent_absorb_kernel<T><<<ga, 128, sm_a, st>>>(*p, ql);                                                                          \
+    latent_absorb_kernel<T><<<ga, 128, sm_a, st>>>(*p, ql, nullptr);                                                                 \
     if (pl.hg == 16) {                                                                                                               \
       if (pl.smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(latent_split_kernel<T, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem)); \
       latent_split_kernel<T, 16><<<gs, SPLIT_T, pl.smem, st>>>(*p, ql, part, pl.n_split, pairs);                                    \
@@ -651,9 +663,10 @@ extern "C" int evo_latent_attn_decode(const evo_latent_decode_params* p, void* w
     latent_uv_kernel<T><<<gu, 256, sm_u, st>>>(*p, ql);
 #define EVO_LATENT_MMA(NV8)                                                                                                          \
     { if (pl.smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(latent_split_mma_kernel<NV8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem)); \
-      latent_split_mma_kernel<NV8><<<gs, 128, pl.smem, st>>>(*p, ql, part, pl.n_split); }
+      latent_split_mma_kernel<NV8><<<gs, 128, pl.smem, st>>>(*p, qsplit, part, pl.n_split); }
     if (pl.mma) {
-      latent_absorb_kernel<bf16><<<ga, 128, sm_a, st>>>(*p, ql);
+      bf16* qsplit = (bf16*)(ql + ((size_t)R * p->H * kw + (size_t)pl.n_split * R * p->H * (p->rank + 2) + 3) / 4 * 4);
+      latent_absorb_kernel<bf16><<<ga, 128, sm_a, st>>>(*p, ql, qsplit);
       switch (p->rank) {
         case 64: EVO_LATENT_MMA(2) break;
         case 128: EVO_LATENT_MMA(4) break;
