@@ -188,16 +188,18 @@ def load_streaming(model, model_dir: str, device) -> Dict[str, int]:
     return {"tensors": len(seen), "bytes": nbytes}
 
 
-def load_named_tensors(model_dir: str, device, shapes: Dict[str, tuple], what: str = "model"):
+def load_named_tensors(model_dir: str, device, shapes: Dict[str, tuple], what: str = "model", ignorable=()):
     """Flat-named checkpoints (one tensor per name, no module tree): every tensor goes mmap -> pinned staging -> device and is
-    checked against `shapes` with the strict-mode rules of load_streaming.  Returns ({name: device tensor}, stats)."""
+    checked against `shapes` with the strict-mode rules of load_streaming.  Names in `ignorable` may be present without being used
+    (tensors of a mechanism the configuration switches off).  Returns ({name: device tensor}, stats)."""
     device = torch.device(device)
     stage = _Staging(device)
     out, unexpected, errors, nbytes = {}, [], [], 0
     for path in shard_files(model_dir):
         for name, dt, shape, raw in iter_safetensors(path):
             if name not in shapes:
-                unexpected.append(name)
+                if name not in ignorable:
+                    unexpected.append(name)
                 continue
             if tuple(shape) != tuple(shapes[name]):
                 errors.append(f"size mismatch for {name}: checkpoint {tuple(shape)}, model {tuple(shapes[name])}")

@@ -104,7 +104,7 @@ def _load_flat(family, model_dir: str, config: dict, device, dtype):
     model = cls(cfg_cls.from_dict(config), dtype=dtype or torch.bfloat16)
     dev = torch.device(device) if device is not None else torch.device("cpu")
     shapes = {k: tuple(v.shape) for k, v in model.weights.items()}
-    tensors, model.ingest_stats = load_named_tensors(model_dir, dev, shapes, type(model).__name__)
+    tensors, model.ingest_stats = load_named_tensors(model_dir, dev, shapes, type(model).__name__, ignorable=getattr(model.config, "unused_tensor_names", ()))
     for name, t in tensors.items():
         model.weights[name] = t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16)
     model._invalidate()

@@ -82,6 +82,11 @@ class MovalornConfig:
     def looped(self) -> bool:
         return self.loop_stop > self.loop_start
 
+    @property
+    def unused_tensor_names(self):
+        """Tensors a checkpoint may carry although this configuration never reads them (a loop over no layers)."""
+        return () if self.looped else ("loop.in", "loop.step")
+
     # dict-style access used by the framework's generic code paths (model.config.get("max_seqlen"))
     def get(self, key, default=None):
         return getattr(self, key, default)

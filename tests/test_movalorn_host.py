@@ -74,6 +74,13 @@ def test_registry_picks_the_class_and_the_loader_is_strict(tmp_path):
         load_model_dir(str(tmp_path / "shape"))
     with pytest.raises(NotImplementedError):
         load_model_dir(str(tmp_path / "ok"), dtype=torch.float16)
+    # a loop over no layers: its tensors may be in the file, nothing reads them
+    flat = O.make_config(loop=(1, 1, 2))
+    Wf = O.random_weights(flat, seed=2)
+    assert "loop.in" not in Wf
+    _write_checkpoint(tmp_path / "flat", flat, dict(Wf, **{"loop.in": W["loop.in"], "loop.step": W["loop.step"]}))
+    m2 = load_model_dir(str(tmp_path / "flat"))
+    assert not m2.config.looped and "loop.in" not in m2.weights and len(m2.config.runs) == len(flat["layers"])
 
 
 def test_model_refuses_to_run_without_cuda():
