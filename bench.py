@@ -624,7 +624,7 @@ def _movalorn_models(size, dev):
     lat = {"type": "latent_attention", "mixer": {"heads": H, "dim": 64, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 1.0 / 128 ** 0.5,
                                                  "mask": {"size": 1024}, "rot": {"base": 10000.0, "dims": 64}}}
     mc = {"architecture": "Movalorn", "vocab": 512, "width": d, "norm": {"eps": 1e-5}, "logit_scale": 1.0,
-          "embedding": {"scale": 1.0, "bigram": {"buckets": 4093, "mul_prev": 31, "mul_cur": 7}},
+          "embedding": {"scale": 1.0, "bigram": {"buckets": 4093, "mul_prev": 13, "mul_cur": 5}},
           "layers": [dict(gru, mlp=dense), dict(lat, mlp=moe), dict(gru, mlp=moe), dict(gru, mlp=dense)]}
     mv = Movalorn(MovalornConfig.from_dict(mc)).init_random(0, device=dev)
     return mv, zv

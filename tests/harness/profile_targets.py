@@ -69,7 +69,7 @@ elif what in ("movalorn", "movalorn_step"):
                                                  "rot": {"base": 10000.0, "dims": 64}},
            "mlp": {"kind": "moe", "expert": {"ff": 1408}, "router": {"experts": 16, "top": 4, "scale": 1.0}, "shared": {"ff": 1408}}}
     mc = {"architecture": "Movalorn", "vocab": 512, "width": 2048, "norm": {"eps": 1e-5}, "logit_scale": 1.0, "layers": [gru, lat],
-          "embedding": {"scale": 1.0, "bigram": {"buckets": 4093, "mul_prev": 31, "mul_cur": 7}}}
+          "embedding": {"scale": 1.0, "bigram": {"buckets": 4093, "mul_prev": 13, "mul_cur": 5}}}
     model = Movalorn(MovalornConfig.from_dict(mc)).init_random(0, device=dev)
     if what == "movalorn":
         ids = torch.randint(0, 512, (2, 4096), device=dev)
