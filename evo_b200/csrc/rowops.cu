@@ -470,6 +470,79 @@ __global__ void __launch_bounds__(256) branch_norm_kernel(evo_branch_norm_params
   }
 }
 
+// The same for rows of at most 16 x blockDim channels on the vector path: a thread keeps its (up to 16) channels in registers from the
+// first read to the last store, so the branch, its gate and the stream are read once and every sigmoid is evaluated once.
+template <typename T>
+__global__ void __launch_bounds__(256) branch_norm_cached_kernel(evo_branch_norm_params p) {
+  __shared__ float red[32];
+  constexpr int NIT = 4;
+  const int64_t r = blockIdx.x;
+  const int64_t srow = p.gather ? p.gather[r] : r;
+  const int D = p.D, step = blockDim.x * 4, c0 = threadIdx.x * 4;
+  float* xr = p.x + srow * D;
+  const T* yr = p.y ? (const T*)p.y + srow * p.ldy : nullptr;
+  const T* gr = (p.y && p.gate) ? (const T*)p.gate + srow * p.ldg : nullptr;
+  const bf16* gb = (const bf16*)p.gate_bias;
+  const bf16* ra = (const bf16*)p.row_add;
+  const bool write_back = p.gather == nullptr && (yr != nullptr || ra != nullptr);
+  float c[NIT][4];
+  float su = 0.f;
+#pragma unroll
+  for (int it = 0; it < NIT; ++it) {
+    const int col = c0 + it * step;
+    c[it][0] = c[it][1] = c[it][2] = c[it][3] = 0.f;
+    if (yr && col < D) {
+      const float4 y4 = ld4(yr + col);
+      c[it][0] = y4.x; c[it][1] = y4.y; c[it][2] = y4.z; c[it][3] = y4.w;
+      if (gr) {
+        const float4 g4 = ld4(gr + col);
+        float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (gb) b4 = ld4(gb + col);
+        c[it][0] *= sigm<T>(g4.x + b4.x); c[it][1] *= sigm<T>(g4.y + b4.y); c[it][2] *= sigm<T>(g4.z + b4.z); c[it][3] *= sigm<T>(g4.w + b4.w);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) su = fmaf(c[it][k], c[it][k], su);
+    }
+  }
+  float mul = 1.f;
+  if (yr && p.post_norm) {
+    su = block_sum(su, red);
+    mul = p.post_gain / sqrtf(su / (float)D + p.eps);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < NIT; ++it) {
+    const int col = c0 + it * step;
+    if (col < D) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (!p.replace) v = ld4(xr + col);
+      v.x = fmaf(c[it][0], mul, v.x); v.y = fmaf(c[it][1], mul, v.y); v.z = fmaf(c[it][2], mul, v.z); v.w = fmaf(c[it][3], mul, v.w);
+      if (ra) { const float4 a4 = ld4(ra + col); v.x += a4.x; v.y += a4.y; v.z += a4.z; v.w += a4.w; }
+      if (write_back) st4(xr + col, v);
+      c[it][0] = v.x; c[it][1] = v.y; c[it][2] = v.z; c[it][3] = v.w;
+      ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+    }
+  }
+  if (!p.out) return;
+  T* orow = (T*)p.out + r * p.ldo;
+  float g = 1.f;
+  if (!p.concat) {
+    ss = block_sum(ss, red);
+    g = p.gain / sqrtf(ss / (float)D + p.eps);
+  }
+#pragma unroll
+  for (int it = 0; it < NIT; ++it) {
+    const int col = c0 + it * step;
+    if (col < D) st4(orow + col, make_float4(c[it][0] * g, c[it][1] * g, c[it][2] * g, c[it][3] * g));
+  }
+  const float* cr = p.concat ? p.cat + srow * D : nullptr;
+  for (int col = D + c0; col < p.ldo; col += step) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (cr && col < 2 * D) v = ld4(cr + col - D);
+    st4(orow + col, v);
+  }
+}
+
 template <typename T>
 __device__ __forceinline__ float act_value(float z, int act) {
   if (act == 0) {                         // tanh form of gelu: 0.5 z (1 + tanh(a)) = z sigmoid(2a)
@@ -537,6 +610,12 @@ extern "C" int evo_branch_norm(const evo_branch_norm_params* p, void* stream) {
   const bool vec = p->D % 4 == 0 && p->ldy % 4 == 0 && p->ldg % 4 == 0 && p->ldo % 4 == 0 && aligned16(p->x) && aligned_to(p->y, av) && aligned_to(p->gate, av) &&
                    aligned_to(p->out, av) && aligned16(p->cat) && aligned_to(p->gate_bias, 8) && aligned_to(p->row_add, 8);
   cudaStream_t st = (cudaStream_t)stream;
+  // few rows (a decoding step): the row stays in registers -- one read, one sigmoid per element, a short dependency chain; many rows run
+  // faster through the three-pass kernel (fewer registers, more rows in flight per SM; its re-reads hit L1)
+  if (vec && p->D <= 16 * (int)block.x && p->rows < 4096) {
+    if (p->dtype) branch_norm_cached_kernel<float><<<grid, block, 0, st>>>(*p); else branch_norm_cached_kernel<bf16><<<grid, block, 0, st>>>(*p);
+    return check_launch("evo_branch_norm");
+  }
   if (p->dtype) { if (vec) branch_norm_kernel<float, true><<<grid, block, 0, st>>>(*p); else branch_norm_kernel<float, false><<<grid, block, 0, st>>>(*p); }
   else { if (vec) branch_norm_kernel<bf16, true><<<grid, block, 0, st>>>(*p); else branch_norm_kernel<bf16, false><<<grid, block, 0, st>>>(*p); }
   return check_launch("evo_branch_norm");

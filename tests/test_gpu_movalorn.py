@@ -57,7 +57,7 @@ def test_pair_embedding_first_token_carried_token_and_batch(ids_dtype):
     assert prev.tolist() == ids[:, -1].tolist()
 
 
-@pytest.mark.parametrize("D,ldo", [(96, 128), (130, 192), (1032, 1088)])
+@pytest.mark.parametrize("D,ldo", [(96, 128), (130, 192), (1032, 1088), (4100, 4160)])
 def test_branch_norm_modes(D, ldo):
     M, eps = 5, 1e-5
     g = torch.Generator().manual_seed(D)
